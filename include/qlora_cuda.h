@@ -47,7 +47,10 @@ extern "C" {
 /* Arithmetic used by the layer GEMMs.
  *  AUTO       : tensor-core path (bf16 operands, fp32 accumulate) when the shape allows it
  *               (block_size 32, 64, 128 or 256, in_dim and out_dim multiples of 64, LoRA rank <= 64),
- *               otherwise the exact fp32 path.
+ *               otherwise the exact fp32 path.  Exception: the reference-named fp32 host entry points
+ *               qlc_qlora_forward / qlc_qlora_backward use TF32 instead of bf16 where the shape allows it,
+ *               so that they keep the reference's GPU-vs-CPU tolerances (max abs diff 1e-3 / 1e-2,
+ *               qlora-wgpu/tests/gpu_parity.rs:59, gpu_backward.rs:88-96) at every shape.
  *  FP32_EXACT : fp32 SIMT kernels that reproduce the reference's CPU accumulation order
  *               bit-for-bit (any shape, any block size).
  *  BF16       : force the tensor-core path; unsupported shapes fail with QLC_ERR_GPU.
@@ -118,6 +121,14 @@ int qlc_qtensor_requantize_dev(qlc_ctx *ctx, qlc_qtensor *q, const float *d_weig
 /* QuantizedTensor::from_raw_parts (qlora-core/src/quant.rs:171-207): plain fp32 scales. */
 int qlc_qtensor_from_raw_parts(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, const uint8_t *codes,
                                size_t codes_len, const float *scales, size_t scales_len, qlc_qtensor **out);
+/* A double-quantised tensor from its stored payload: packed nibbles, the 8-bit absmax codes and the fp32
+ * second-level absmax, exactly the three arrays of ScaleStore::Int8 (qlora-core/src/quant.rs:84-101) that
+ * qlc_qtensor_codes / _absmax_codes / _absmax2 return.  The reference has no constructor for this form (its
+ * from_raw_parts always yields fp32 scales, quant.rs:171-207); this one lets a saved NF4 payload come back
+ * bit for bit, 8-bit scales included.  Length checks as from_raw_parts, plus absmax2_len == ceil(blocks/256). */
+int qlc_qtensor_from_double_quant_parts(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, const uint8_t *codes,
+                                        size_t codes_len, const uint8_t *absmax_codes, size_t absmax_codes_len,
+                                        const float *absmax2, size_t absmax2_len, qlc_qtensor **out);
 int qlc_qtensor_destroy(qlc_qtensor *q);
 
 typedef struct qlc_qtensor_info {
@@ -227,7 +238,9 @@ int qlc_qlora_backward_dev(qlc_ctx *ctx, qlc_layer *layer, const void *d_x, cons
  *    in_dim and out_dim multiples of 64, rank <= 64).
  *  - The call makes no cudaMalloc, cudaFree or other allocating CUDA call.  The first call on each
  *    device additionally looks up the array's device address (cudaGetSymbolAddress); make that first
- *    call during start-up, before any stream capture.
+ *    call during start-up, before any stream capture.  The two diagnostics of this library do allocate
+ *    and must stay off for this guarantee: per-kernel timing (qlc_ctx_profile_enable creates CUDA
+ *    events as it goes) and the QLC_GEMM_TIMING environment variable (a device buffer per launch).
  *  - All calls on a device share the one array, in every context and stream.  Two such calls whose
  *    kernels overlap on the GPU race on it; serialise them (one stream, or events).  Nothing has to be
  *    cleared between calls: each call rewrites every scratch row it later reads. */
@@ -276,6 +289,13 @@ size_t qlc_adam_state_bytes(const qlc_adam *opt);
  * Any output pointer may be NULL. */
 int qlc_adam_get_state(qlc_adam *opt, size_t index, size_t *numel, uint64_t *step, uint8_t *m_codes,
                        uint8_t *v_codes, float *m_scales, float *v_scales);
+/* Restores the raw state of tensor `index` (the inverse of qlc_adam_get_state; ParamState, optim.rs:104-126):
+ * numel elements, the tensor's step counter, and the four arrays with the lengths qlc_adam_get_state
+ * documents.  States are restored in order: `index` may name an existing state (replaced, re-created when
+ * numel differs) or the next one to be created.  A step after restoring continues bit for bit as if the
+ * optimiser had never been saved.  (The reference keeps ParamState private and has no save / restore.) */
+int qlc_adam_set_state(qlc_adam *opt, size_t index, size_t numel, uint64_t step, const uint8_t *m_codes,
+                       const uint8_t *v_codes, const float *m_scales, const float *v_scales);
 /* Bytes of optimiser state currently resident in device memory / parked in pinned host memory,
  * and the number of bytes the last step moved over the host link in each direction. */
 int qlc_adam_paging_info(const qlc_adam *opt, size_t *device_bytes, size_t *host_bytes, size_t *h2d_bytes_last_step,
@@ -376,6 +396,29 @@ int qlc_llama_train_step_dp(qlc_llama *model, qlc_adam *adam, qlc_comm *comm, co
                             size_t n_seq, size_t seq_len, float *loss);
 int qlc_llama_adapter_grads(qlc_llama *model, size_t layer, int kind, float *grad_a, float *grad_b);
 int qlc_llama_adapter_weights(qlc_llama *model, size_t layer, int kind, float *a, float *b);
+
+/* ---- self-tests (no counterpart in the reference) ----------------------------------------------------- */
+
+/* Runs the quantise kernels' code-selection routine (15 decision thresholds on the divided target) over the
+ * `count` consecutive fp32 bit patterns starting at `first_bits`, read as targets t = w / absmax, and returns
+ * the codes two per byte (pattern first_bits + 2i in the low nibble of out[i]); out_len == ceil(count / 2).
+ * The parity tests compare this with the 16-way scan of qlora-core/src/quant.rs:263-278 for EVERY target in
+ * [-1, 1]. */
+int qlc_selftest_nf4_codes_of_targets(qlc_ctx *ctx, uint32_t first_bits, size_t count, uint8_t *out, size_t out_len);
+/* Runs the block-64 quantise kernel's fast code selection (approximate quotient w * rcp(absmax), 32-bin table,
+ * exact redo inside a guard band around the bin's threshold) for every weight bit pattern in
+ * [first_bits, first_bits + count) against the block absmax `absmax`, and compares each code with the code of
+ * the IEEE quotient w / absmax (what quant.rs:264 computes), on the device.  Returns the number of differing
+ * weights (must be 0), the number of 8-weight groups that took the exact redo, and the first differing bit
+ * pattern. */
+int qlc_selftest_nf4_fast_path(qlc_ctx *ctx, float absmax, uint32_t first_bits, uint64_t count, uint64_t *mismatches,
+                               uint64_t *redone, uint32_t *first_mismatch_bits);
+/* Failure-path test: enqueues a one-CTA kernel (no TMA, no tensor memory) whose thread 0 waits, with the
+ * bounded wait of the tensor-core kernels, on an mbarrier nobody arrives on.  After `limit_cycles` SM clock
+ * cycles (1 .. 1e8) the wait gives up, stores (code 1, site 99, block 0) in the context's status word and the
+ * kernel returns normally.  Tensor-core kernels queued behind it return at once; the next
+ * qlc_ctx_synchronize fails with QLC_ERR_GPU naming the site, clears the status, and the context works again. */
+int qlc_selftest_wait_timeout(qlc_ctx *ctx, uint64_t limit_cycles);
 
 #ifdef __cplusplus
 }

@@ -51,6 +51,7 @@ def _declare(l):
     l.orc_nearest_nf4_code.argtypes = [C.c_float, C.c_float]
     l.orc_nf4_code_of_target.restype = C.c_uint8
     l.orc_nf4_code_of_target.argtypes = [C.c_float]
+    l.orc_nf4_codes_of_target_bits.argtypes = [C.c_uint32, _sz, _u8p, C.c_int]
     l.orc_double_quantize_scales.argtypes = [_f32p, _sz, _u8p, _f32p]
     l.orc_quantize_nf4.argtypes = [_f32p, _sz, _sz, C.c_int, _u8p, _f32p, C.c_void_p, C.c_void_p]
     l.orc_block_scales_dq.argtypes = [_u8p, _f32p, _sz, _f32p]
@@ -157,6 +158,22 @@ def nearest_nf4_code(w: float, absmax: float) -> int:
 
 def nf4_code_of_target(t: float) -> int:
     return int(lib().orc_nf4_code_of_target(np.float32(t)))
+
+
+def nf4_codes_of_target_bits(first_bits: int, count: int, threads: int = 0) -> np.ndarray:
+    """The 16-way scan (quant.rs:263-278) for `count` consecutive fp32 bit patterns read as targets,
+    two codes per byte (low nibble first)."""
+    out = np.empty((count + 1) // 2, np.uint8)
+    lib().orc_nf4_codes_of_target_bits(first_bits, count, out, threads or max(max_threads(), len(os.sched_getaffinity(0))))
+    return out
+
+
+def block_scales_dq(absmax_codes, absmax2) -> np.ndarray:
+    """quant.rs:212-221 on raw parts: (code as i8 as f32) / 127 * absmax2[block / 256]."""
+    ac = np.ascontiguousarray(absmax_codes, np.uint8)
+    out = np.empty(ac.size, np.float32)
+    lib().orc_block_scales_dq(ac, _f32(absmax2), ac.size, out)
+    return out
 
 
 def matmul(a, b, m, k, n, threads=1):

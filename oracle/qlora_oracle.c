@@ -104,6 +104,26 @@ uint8_t orc_nf4_code_of_target(float target) {
     return best;
 }
 
+/* The scan above for `count` consecutive fp32 bit patterns read as targets, two codes per output byte
+ * (pattern first_bits + 2i in the low nibble of out[i]); OpenMP over chunks.  Used by the exhaustive sweep
+ * that compares the CUDA kernels' code selection with quant.rs:263-278 for every target in [-1, 1]. */
+void orc_nf4_codes_of_target_bits(uint32_t first_bits, size_t count, uint8_t *out, int threads) {
+    const ptrdiff_t bytes = (ptrdiff_t)((count + 1) / 2);
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+    for (ptrdiff_t b = 0; b < bytes; ++b) {
+        uint8_t v = 0;
+        for (int h = 0; h < 2; ++h) {
+            const size_t i = 2 * (size_t)b + (size_t)h;
+            if (i >= count) break;
+            const uint32_t bits = first_bits + (uint32_t)i;
+            float t;
+            memcpy(&t, &bits, 4);
+            v |= (uint8_t)(orc_nf4_code_of_target(t) << (4 * h));
+        }
+        out[b] = v;
+    }
+}
+
 /* quant.rs:283-299 — int8 double quantisation of the block scales. */
 void orc_double_quantize_scales(const float *scales, size_t nb, uint8_t *codes, float *absmax2) {
     size_t nsb = (nb + ORC_DOUBLE_QUANT_BLOCK - 1) / ORC_DOUBLE_QUANT_BLOCK;

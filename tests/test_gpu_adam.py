@@ -174,3 +174,82 @@ def test_forced_eviction_mixed_sizes_bitwise(v, oracle):
             assert np.array_equal(p1[i].view(np.uint32), p2[i].view(np.uint32)), (t, i, sizes[i])
     info = paged.paging_info()
     assert info["h2d_bytes_last_step"] == info["d2h_bytes_last_step"] == paged.state_bytes()
+
+
+def test_state_save_restore_continues_bitwise(v, oracle):
+    """Checkpointing: get_state of every tensor, restored into a fresh optimiser with set_state, then both take
+    more steps - parameters and state stay bit-identical (ParamState, optim.rs:104-126).  Once resident, once
+    with the state parked in pinned host memory (max_resident_pages=2)."""
+    sizes = [1000, 77, 4096 + 13, 70000]
+    for pages in (None, 2):
+        a = v.Adam8bit(v.AdamConfig(max_resident_pages=pages))
+        pa = [normal(30 + i, n, 0.01) for i, n in enumerate(sizes)]
+        for t in range(3):
+            a.step(pa, [normal(500 * t + i, n, 0.01) for i, n in enumerate(sizes)])
+        saved = [a.get_state(i) for i in range(len(sizes))]
+        assert all(s["step"] == 3 for s in saved)
+        b = v.Adam8bit(v.AdamConfig(max_resident_pages=pages))
+        for i, s in enumerate(saved):
+            b.set_state(i, s)
+        assert b.state_bytes() == a.state_bytes()
+        pb = [p.copy() for p in pa]
+        for t in range(3, 6):
+            g = [normal(500 * t + i, n, 0.01) for i, n in enumerate(sizes)]
+            a.step(pa, g)
+            b.step(pb, g)
+            for i in range(len(sizes)):
+                assert np.array_equal(pa[i].view(np.uint32), pb[i].view(np.uint32)), (pages, t, i)
+        for i in range(len(sizes)):
+            sa, sb = a.get_state(i), b.get_state(i)
+            assert sa["step"] == sb["step"] == 6
+            for k in ("m_codes", "v_codes", "m_scales", "v_scales"):
+                assert np.array_equal(sa[k], sb[k]), (pages, i, k)
+        # replacing a state in place (same index) and wrong orders / sizes
+        b.set_state(1, saved[1])
+        assert b.get_state(1)["step"] == 3
+        with pytest.raises(v.ShapeMismatch):
+            v.Adam8bit().set_state(2, saved[2])  # index 2 before 0 and 1
+        bad = dict(saved[0], m_codes=saved[0]["m_codes"][:-1])
+        with pytest.raises(v.ShapeMismatch):
+            b.set_state(0, bad)
+
+
+def test_full_size_config3_bitwise(v, oracle):
+    """BASELINE config 3 at full size: 112 tensors x 262 144 fp32 (28 layers x Q/V x {A 64x4096, B 4096x64}),
+    block 256, 3 steps, fully resident and with max_resident_pages=4 (every page evicted to pinned host memory
+    each step), on device buffers as the benchmark runs it.  Parameters and 8-bit state of both runs equal the
+    CPU oracle's bit for bit; the oracle steps a sample of the tensors (all tensors are independent)."""
+    import torch
+
+    n_t, numel = 112, 262144
+    dev = torch.device("cuda", 0)
+    ctx = v.GpuContext(0)
+    host_p = [normal(6000 + i, numel, 0.01) for i in range(n_t)]
+    runs = {}
+    for name, pages in (("resident", None), ("paged", 4)):
+        opt = v.Adam8bit(v.AdamConfig(max_resident_pages=pages), ctx)
+        params = [torch.from_numpy(p).to(dev) for p in host_p]
+        for t in range(3):
+            grads = [torch.from_numpy(normal(7000 + 1000 * t + i, numel, 0.01)).to(dev) for i in range(n_t)]
+            torch.cuda.synchronize()
+            st = opt.step_dev([p.data_ptr() for p in params], [g.data_ptr() for g in grads], [numel] * n_t)
+            ctx.synchronize()
+            assert st.pages_streamed == n_t * numel // 256 and st.state_bytes == 59637760
+        runs[name] = (opt, [p.cpu().numpy() for p in params])
+    info = runs["paged"][0].paging_info()
+    assert info["host_bytes"] == 59637760 and info["h2d_bytes_last_step"] == 59637760
+    for i in range(n_t):
+        assert np.array_equal(runs["resident"][1][i].view(np.uint32), runs["paged"][1][i].view(np.uint32)), i
+    sample = [0, 1, 55, 110, 111]
+    for i in sample:
+        oopt = oracle.Adam8bit()
+        p = [host_p[i].copy()]
+        for t in range(3):
+            oopt.step(p, [normal(7000 + 1000 * t + i, numel, 0.01)])
+        for name in runs:
+            assert np.array_equal(runs[name][1][i].view(np.uint32), p[0].view(np.uint32)), (name, i)
+            st, os_ = runs[name][0].get_state(i), oopt.states[0]
+            assert st["step"] == 3
+            assert np.array_equal(st["m_codes"], os_["m_codes"]) and np.array_equal(st["v_codes"], os_["v_codes"])
+            assert np.array_equal(st["m_scales"].view(np.uint32), os_["m_scales"].view(np.uint32))
+            assert np.array_equal(st["v_scales"].view(np.uint32), os_["v_scales"].view(np.uint32))

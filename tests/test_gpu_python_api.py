@@ -105,3 +105,29 @@ def test_paged_adam_trains_adapter_downhill(qlora_wgpu):
         a, b = opt.step([a, b], [g.grad_a, g.grad_b])
     assert mse(a, b) < before
     assert opt.state_bytes() < 8 * (len(a) + len(b))
+
+
+def test_eligible_shape_keeps_the_reference_gpu_tolerances(qlora_wgpu, oracle):
+    """256x256 with r=16 is a shape the tensor-core path takes.  The drop-in module offers no precision switch,
+    so its results must keep the reference's own GPU-vs-CPU contract at such a shape too: max abs diff < 1e-3
+    for the forward pass (qlora-wgpu/tests/gpu_parity.rs:59) and < 1e-2 for the gradients
+    (qlora-wgpu/tests/gpu_backward.rs:88-96).  bf16 operands would not; the fp32 entry points compute in TF32."""
+    import numpy as np
+
+    from refdata import normal
+
+    out_dim = in_dim = 256
+    r, batch, alpha = 16, 64, 32.0
+    w = normal(1, out_dim * in_dim, 0.02)
+    a, b = normal(2, r * in_dim, 1.0 / 16.0), normal(3, out_dim * r, 0.01)
+    x, dy = normal(4, batch * in_dim, 1.0), normal(5, batch * out_dim, 1.0)
+    q = qlora_wgpu.quantize_nf4(w.tolist(), out_dim, in_dim)
+    y = np.array(qlora_wgpu.qlora_linear_forward(x.tolist(), batch, q, a.tolist(), b.tolist(), alpha, use_gpu=True), np.float32)
+    g = qlora_wgpu.qlora_linear_backward(x.tolist(), dy.tolist(), batch, q, a.tolist(), b.tolist(), alpha, use_gpu=True)
+    wd = oracle.quantize_nf4(w, out_dim, in_dim).dequantize()
+    assert np.array_equal(np.array(q.dequantize(), np.float32), wd)  # GPU dequantise of the exported fields
+    y_ref = oracle.qlora_forward(x, batch, wd, out_dim, in_dim, a, b, r, alpha)
+    gx_ref, ga_ref, gb_ref = oracle.qlora_backward(x, dy, batch, wd, out_dim, in_dim, a, b, r, alpha)
+    assert np.max(np.abs(y - y_ref)) < 1e-3
+    for got, ref in ((g.grad_x, gx_ref), (g.grad_a, ga_ref), (g.grad_b, gb_ref)):
+        assert np.max(np.abs(np.array(got, np.float32) - ref)) < 1e-2

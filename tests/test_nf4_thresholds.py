@@ -68,7 +68,7 @@ def test_fast_path_bin_table(oracle):
     least the kernel's 1e-6 guard band (closer ones are redone exactly by the kernel)."""
     src = open(os.path.join(ROOT, "vkqlora", "rs_b200", "csrc", "quant_kernels.cu")).read()
     scale = np.float32(re.search(r"kBinScale\s*=\s*([0-9.]+)f", src).group(1))
-    m = re.search(r"\(t & 16\) \? (0x[0-9A-Fa-f]+)ull : (0x[0-9A-Fa-f]+)ull", src)
+    m = re.search(r"\(lane & 16\) \? (0x[0-9A-Fa-f]+)ull : (0x[0-9A-Fa-f]+)ull", src)
     hi, lo = int(m.group(1), 16), int(m.group(2), 16)
     ks = [(lo >> (4 * i)) & 15 for i in range(16)] + [(hi >> (4 * i)) & 15 for i in range(16)]
     thr = np.array(_kernel_thresholds(), np.uint32).view(np.float32)

@@ -183,6 +183,21 @@ class QuantizedTensor:
         check(lib.qlc_qtensor_from_raw_parts(ctx._h, rows, cols, block_size, _p(c), c.size, _p(s), s.size, C.byref(h)))
         return cls(h, ctx)
 
+    @classmethod
+    def from_double_quant_parts(cls, rows: int, cols: int, block_size: int, codes, absmax_codes, absmax2,
+                                ctx: Optional[GpuContext] = None) -> "QuantizedTensor":
+        """A double-quantised tensor from its stored payload (what codes() / absmax_codes() / absmax2() return):
+        the 8-bit scales come back as they were, unlike from_raw_parts, which takes decoded fp32 scales."""
+        ctx = ctx or default_context()
+        c = np.ascontiguousarray(np.frombuffer(bytes(codes), dtype=np.uint8) if isinstance(codes, (bytes, bytearray))
+                                 else np.asarray(codes, dtype=np.uint8))
+        ac = np.ascontiguousarray(absmax_codes, dtype=np.uint8).reshape(-1)
+        a2 = _f32(absmax2)
+        h = C.c_void_p()
+        check(lib.qlc_qtensor_from_double_quant_parts(ctx._h, rows, cols, block_size, _p(c), c.size, _p(ac), ac.size,
+                                                      _p(a2), a2.size, C.byref(h)))
+        return cls(h, ctx)
+
     # accessors, quant.rs:224-258
     def rows(self) -> int: return self._info.rows
     def cols(self) -> int: return self._info.cols
@@ -339,6 +354,9 @@ class QloraLinear:
         """Host buffers in `dtype` (bf16 as uint16 bit patterns); copies are part of the call."""
         es = np.uint16 if dtype == DTYPE_BF16 else np.float32
         x = np.ascontiguousarray(x, dtype=es).reshape(-1)
+        if x.size != batch * self.in_dim():  # the C call takes no lengths: a short array would be read past its end
+            raise ShapeMismatch(_lib.ERR_SHAPE_MISMATCH,
+                                f"shape mismatch: x.len() = {x.size} but batch*in_dim = {batch * self.in_dim()}")
         y = np.empty(batch * self.out_dim(), es)
         check(lib.qlc_qlora_forward_host(self._ctx._h, self._h, _p(x), dtype, batch, _p(y)))
         return y
@@ -560,6 +578,17 @@ class Adam8bit:
         ms, vs = np.empty(nb, np.float32), np.empty(nb, np.float32)
         check(lib.qlc_adam_get_state(self._h, index, None, None, _p(mc), _p(vc), _p(ms), _p(vs)))
         return dict(numel=n, step=step.value, m_codes=mc, v_codes=vc, m_scales=ms, v_scales=vs)
+
+    def set_state(self, index: int, state: dict) -> None:
+        """Restores what get_state(index) returned (checkpoint restore); states are restored in order."""
+        mc = np.ascontiguousarray(state["m_codes"], np.uint8)
+        vc = np.ascontiguousarray(state["v_codes"], np.uint8)
+        ms, vs = _f32(state["m_scales"]), _f32(state["v_scales"])
+        n = int(state["numel"])
+        nb = (n + self._block_size - 1) // self._block_size
+        if mc.size != n or vc.size != n or ms.size != nb or vs.size != nb:
+            raise ShapeMismatch(_lib.ERR_SHAPE_MISMATCH, "shape mismatch: state arrays do not match numel / block_size")
+        check(lib.qlc_adam_set_state(self._h, index, n, int(state["step"]), _p(mc), _p(vc), _p(ms), _p(vs)))
 
     def paging_info(self):
         vals = [C.c_size_t() for _ in range(4)]

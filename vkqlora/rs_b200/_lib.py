@@ -56,6 +56,7 @@ SIGNATURES = {
     "qlc_quantize_nf4_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _pp]),
     "qlc_qtensor_requantize_dev": (_i, [_vp, _vp, _vp]),
     "qlc_qtensor_from_raw_parts": (_i, [_vp, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _pp]),
+    "qlc_qtensor_from_double_quant_parts": (_i, [_vp, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _pp]),
     "qlc_qtensor_destroy": (_i, [_vp]),
     "qlc_qtensor_get_info": (_i, [_vp, C.POINTER(QTensorInfo)]),
     "qlc_qtensor_codes": (_i, [_vp, _vp, _sz]),
@@ -94,6 +95,7 @@ SIGNATURES = {
     "qlc_adam_set_fast_math": (_i, [_vp, _i]),
     "qlc_adam_state_bytes": (_sz, [_vp]),
     "qlc_adam_get_state": (_i, [_vp, _sz, C.POINTER(_sz), C.POINTER(C.c_uint64), _vp, _vp, _vp, _vp]),
+    "qlc_adam_set_state": (_i, [_vp, _sz, _sz, C.c_uint64, _vp, _vp, _vp, _vp]),
     "qlc_adam_paging_info": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "qlc_llama_create": (_i, [_vp, _vp, _vp, _vp, _pp]),
     "qlc_llama_destroy": (_i, [_vp]),
@@ -115,6 +117,10 @@ SIGNATURES = {
     "qlc_comm_nranks": (_i, [_vp]),
     "qlc_comm_context": (_vp, [_vp]),
     "qlc_comm_destroy": (_i, [_vp]),
+    "qlc_selftest_nf4_codes_of_targets": (_i, [_vp, C.c_uint32, _sz, _vp, _sz]),
+    "qlc_selftest_nf4_fast_path": (_i, [_vp, C.c_float, C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64),
+                                        C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
+    "qlc_selftest_wait_timeout": (_i, [_vp, C.c_uint64]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

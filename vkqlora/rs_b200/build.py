@@ -27,6 +27,7 @@ SOURCES = {
     "comm.cu": [],
     "llama.cu": [],
     "attention_tc.cu": [],
+    "selftest.cu": [],
 }
 
 

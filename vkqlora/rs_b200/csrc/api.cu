@@ -426,6 +426,39 @@ int qlc_qtensor_from_raw_parts(qlc_ctx *ctx, size_t rows, size_t cols, size_t bl
     return QLC_OK;
 }
 
+int qlc_qtensor_from_double_quant_parts(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, const uint8_t *codes,
+                                        size_t codes_len, const uint8_t *absmax_codes, size_t absmax_codes_len,
+                                        const float *absmax2, size_t absmax2_len, qlc_qtensor **out) {
+    if (!ctx || !out) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    if (block_size == 0) return fail(QLC_ERR_INVALID_CONFIG, "block_size must be > 0");
+    size_t n = 0;
+    if (mul_overflows(rows, cols, &n)) return fail(QLC_ERR_INVALID_CONFIG, "rows*cols overflow");
+    const size_t nb = ceil_div(n, block_size), n2 = ceil_div(nb, kDoubleQuantBlock);
+    if (codes_len != (n + 1) / 2)
+        return fail(QLC_ERR_SHAPE_MISMATCH, "codes.len() = %zu but ceil(rows*cols/2) = %zu", codes_len, (n + 1) / 2);
+    if (absmax_codes_len != nb)
+        return fail(QLC_ERR_SHAPE_MISMATCH, "absmax_codes.len() = %zu but ceil(rows*cols/block_size) = %zu",
+                    absmax_codes_len, nb);
+    if (absmax2_len != n2)
+        return fail(QLC_ERR_SHAPE_MISMATCH, "absmax2.len() = %zu but ceil(num_blocks/256) = %zu", absmax2_len, n2);
+    if ((codes_len && !codes) || (nb && !absmax_codes) || (n2 && !absmax2))
+        return fail(QLC_ERR_INVALID_CONFIG, "null payload");
+    QLC_CUDA(cudaSetDevice(ctx->device));
+    qlc_qtensor *q = nullptr;
+    QLC_TRY(alloc_qtensor(ctx, rows, cols, block_size, true, &q));
+    cudaError_t e = cudaSuccess;
+    if (codes_len) e = cudaMemcpyAsync(q->d_codes, codes, codes_len, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess && nb) e = cudaMemcpyAsync(q->d_absmax_codes, absmax_codes, nb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess && n2) e = cudaMemcpyAsync(q->d_absmax2, absmax2, n2 * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        qlc_qtensor_destroy(q);
+        return fail(QLC_ERR_GPU, "upload of the payload: %s", cudaGetErrorString(e));
+    }
+    *out = q;
+    return QLC_OK;
+}
+
 int qlc_qtensor_destroy(qlc_qtensor *q) {
     if (!q) return QLC_OK;
     if (--q->refs > 0) return QLC_OK;
@@ -744,6 +777,15 @@ int qlc_layer_grad_bucket(qlc_layer *L, float **d_bucket, size_t *n_floats) {
     return QLC_OK;
 }
 
+// Handles are bound to the device they were created on: a layer of another GPU's context would make this
+// GPU's kernels dereference foreign device pointers.
+static int same_device(const qlc_ctx *ctx, const qlc_layer *L) {
+    if (L->ctx->device != ctx->device || L->w->device != ctx->device)
+        return fail(QLC_ERR_GPU, "layer lives on device %d (weight on %d), context on %d", L->ctx->device, L->w->device,
+                    ctx->device);
+    return QLC_OK;
+}
+
 // Which arithmetic a call uses (see QLC_PRECISION_* in the header).
 static int pick_path(qlc_ctx *ctx, const qlc_layer *L, bool *use_umma) {
     const bool ok = umma_supported(L);
@@ -766,6 +808,7 @@ static inline size_t a256(size_t b) { return (b + 255) & ~(size_t)255; }
 
 int qlc_qlora_forward_dev(qlc_ctx *ctx, qlc_layer *L, const void *d_x, int dtype, size_t batch, void *d_y) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
     if (dtype != QLC_DTYPE_F32 && dtype != QLC_DTYPE_BF16) return fail(QLC_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
     if (batch == 0 || L->out_dim == 0) return QLC_OK;
     if (!d_y || (L->in_dim && !d_x)) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
@@ -811,6 +854,7 @@ int qlc_qlora_forward_dev(qlc_ctx *ctx, qlc_layer *L, const void *d_x, int dtype
 
 int qlc_qlora_forward_dev_noalloc(qlc_ctx *ctx, qlc_layer *L, const void *d_x, size_t batch, void *d_y) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
     if (batch == 0 || L->out_dim == 0) return QLC_OK;
     if (!d_x || !d_y) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
     if (!umma_supported(L))
@@ -825,6 +869,7 @@ int qlc_qlora_forward_dev_noalloc(qlc_ctx *ctx, qlc_layer *L, const void *d_x, s
 int qlc_qlora_backward_dev(qlc_ctx *ctx, qlc_layer *L, const void *d_x, const void *d_dy, int dtype, size_t batch,
                            void *d_gx, float *d_ga, float *d_gb) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
     if (dtype != QLC_DTYPE_F32 && dtype != QLC_DTYPE_BF16) return fail(QLC_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
     QLC_CUDA(cudaSetDevice(ctx->device));
     bool use_umma = false;
@@ -935,6 +980,7 @@ static int finish_pipelined(qlc_ctx *ctx) {
 
 int qlc_qlora_forward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, int dtype, size_t batch, void *y) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
     if (dtype != QLC_DTYPE_F32 && dtype != QLC_DTYPE_BF16) return fail(QLC_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
     const size_t es = dtype_size(dtype), nx = batch * L->in_dim, ny = batch * L->out_dim;
     if (ny == 0) return QLC_OK;
@@ -976,6 +1022,7 @@ int qlc_qlora_forward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, int dtype,
 int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype, size_t batch,
                             void *grad_x, float *grad_a, float *grad_b) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
     if (dtype != QLC_DTYPE_F32 && dtype != QLC_DTYPE_BF16) return fail(QLC_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
     const size_t es = dtype_size(dtype), nx = batch * L->in_dim, ny = batch * L->out_dim;
     const size_t na = L->r * L->in_dim, nb = L->out_dim * L->r;
@@ -1024,10 +1071,26 @@ int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const voi
     return finish_pipelined(ctx);
 }
 
+// The reference-named fp32 entry points (qlc_qlora_forward / qlc_qlora_backward) promise the reference's
+// GPU-vs-CPU agreement (max abs diff < 1e-3 forward, < 1e-2 gradients: qlora-wgpu/tests/gpu_parity.rs:59,
+// gpu_backward.rs:88-96), which bf16 operands do not keep at in_dim in the thousands.  Under
+// QLC_PRECISION_AUTO they therefore compute in TF32 where the tensor-core path takes the shape and in exact
+// fp32 elsewhere, so the precision class does not change with the shape; bf16 is an explicit choice
+// (qlc_ctx_set_precision) or comes with the bf16 / device entry points.
+struct Fp32CallPrecision {
+    qlc_ctx *ctx;
+    int saved;
+    Fp32CallPrecision(qlc_ctx *c, const qlc_layer *L) : ctx(c), saved(c->precision) {
+        if (saved == QLC_PRECISION_AUTO) ctx->precision = umma_supported(L) ? QLC_PRECISION_TF32 : QLC_PRECISION_FP32_EXACT;
+    }
+    ~Fp32CallPrecision() { ctx->precision = saved; }
+};
+
 int qlc_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const float *x, size_t x_len, size_t batch, float *y) {
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
     if (x_len != batch * L->in_dim)  // qlora.rs:89-95
         return fail(QLC_ERR_SHAPE_MISMATCH, "x.len() = %zu but batch*in_dim = %zu", x_len, batch * L->in_dim);
+    const Fp32CallPrecision scope(ctx, L);
     return qlc_qlora_forward_host(ctx, L, x, QLC_DTYPE_F32, batch, y);
 }
 
@@ -1038,6 +1101,7 @@ int qlc_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const float *x, size_t x_len,
         return fail(QLC_ERR_SHAPE_MISMATCH, "x.len() = %zu but batch*in_dim = %zu", x_len, batch * L->in_dim);
     if (dy_len != batch * L->out_dim)  // qlora.rs:126-132
         return fail(QLC_ERR_SHAPE_MISMATCH, "dy.len() = %zu but batch*out_dim = %zu", dy_len, batch * L->out_dim);
+    const Fp32CallPrecision scope(ctx, L);
     return qlc_qlora_backward_host(ctx, L, x, dy, QLC_DTYPE_F32, batch, grad_x, grad_a, grad_b);
 }
 

@@ -144,6 +144,11 @@ int launch_pad_to_bf16(qlc_ctx *ctx, const float *d_in, size_t rows, size_t cols
 int launch_pad_transpose_to_bf16(qlc_ctx *ctx, const float *d_in, size_t rows, size_t cols, __nv_bfloat16 *d_out,
                                  size_t cols_pad, size_t rows_pad);
 
+// self-tests of the code selection (quant_kernels.cu)
+int selftest_codes_of_targets(qlc_ctx *ctx, uint32_t first_bits, size_t count, uint8_t *d_out);
+int selftest_fast_path(qlc_ctx *ctx, float absmax, uint32_t first_bits, unsigned long long count,
+                       unsigned long long *d_out3);
+
 // gemm_exact.cu — fp32 SIMT, reference accumulation order
 int exact_matmul(qlc_ctx *ctx, const float *d_a, const float *d_b, size_t m, size_t k, size_t n, float *d_c);
 int exact_matmul_trans_b(qlc_ctx *ctx, const float *d_a, const float *d_b, size_t m, size_t k, size_t n, float *d_c);

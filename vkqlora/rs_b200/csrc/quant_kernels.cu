@@ -91,6 +91,63 @@ __device__ __forceinline__ float decode_scale(bool dq, const uint8_t *__restrict
     return __fmul_rn(__fdiv_rn(c, 127.0f), absmax2[blk / kDoubleQuantBlock]);
 }
 
+// ---- the fast path of the code selection ---------------------------------------------------------
+// Lane b of a warp holds bin b of a 32-entry table: targets with int(t * kBinScale + 16) == b can only be
+// decided by threshold bin_k (every other threshold is more than 1e-3 outside the bin), so the code is
+// bin_k + (t >= T[bin_k]).  32 bins of width 1/16 over [-1, 1]; adjacent thresholds are >= 0.08 apart.
+constexpr float kBinScale = 15.9999f;
+__device__ __forceinline__ void nf4_bin_entry(int lane, const float *s_thr, float &bin_thr, uint32_t &bin_k) {
+    bin_k = (uint32_t)(((lane & 16) ? 0xEEEEDDDCCBBA9887ull : 0x6554432221110000ull) >> (4 * (lane & 15))) & 15u;
+    bin_thr = s_thr[bin_k];
+}
+
+// The eight codes (packed, element j in bits 4j..4j+3) of eight weights of one block with absmax `am`.
+// All 32 lanes of the warp must call this together (the bin table is read with shuffles).
+// Fast path: classify the approximate target ta = w * (1/absmax), which lies within 3e-7 of the exact
+// quotient, against the one decision threshold its bin can reach.  If every ta of the thread stays at
+// least 1e-6 away from its threshold, the exact quotient falls on the same side and the codes stand;
+// otherwise (about one thread in 10^4) the eight codes are redone with the correctly rounded quotient
+// (`redone` reports that, for the self-test's statistics).
+__device__ __forceinline__ uint32_t nf4_pack8(const float (&v)[8], float am, float bin_thr, uint32_t bin_k,
+                                              const float *s_thr, bool &redone) {
+    const bool normal = am > 1e-30f && am < 1e30f;
+    float ra;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(normal ? am : 1.0f));
+    uint32_t packed = 0;
+    float nearest = 1.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float ta = __fmul_rn(v[j], ra);
+        const int bin = __float2int_rz(__fmaf_rn(ta, kBinScale, 16.0f));  // NaN -> bin 0 -> code 0, as the scan
+        const float thr = __shfl_sync(0xffffffffu, bin_thr, bin);
+        const uint32_t k = __shfl_sync(0xffffffffu, bin_k, bin);
+        const float d = __fsub_rn(ta, thr);
+        nearest = fminf(nearest, fabsf(d));
+        packed |= (k + (d >= 0.0f ? 1u : 0u)) << (4 * j);
+    }
+    redone = false;
+    if (normal && nearest < 1e-6f) {
+        // target = w/absmax through the block's reciprocal: q = RN(w*rd), exact residual, one correction
+        // (Markstein) - correctly rounded whenever the quotient is a normal number, and every decision
+        // threshold is at |t| >= 0.0398, far above the range where it is not.
+        const float rd = __frcp_rn(am);
+        packed = 0;
+        redone = true;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float q = __fmul_rn(v[j], rd);
+            const float t = __fmaf_rn(__fmaf_rn(-q, am, v[j]), rd, q);
+            packed |= nf4_code_bsearch(t, s_thr) << (4 * j);
+        }
+    } else if (!normal) {
+        // zero block (code 7), or an absmax at the ends of the exponent range / infinite: IEEE division
+        packed = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) packed |= nf4_code(v[j], am) << (4 * j);
+    }
+    return packed;
+}
+
 // ---- quantise, block 64: one CTA per super-block of 256 blocks (16384 elements) ---------------
 // 8 consecutive lanes own one 64-element block (8 elements each, two 128-bit loads), the block
 // absmax is an 8-lane butterfly, each thread emits one packed 32-bit word of codes.  The 256
@@ -111,12 +168,9 @@ quantize_nf4_b64_kernel(const float *__restrict__ w, size_t n, size_t nb, uint8_
     const size_t base = sb * 16384;
     if (t < 15) s_thr[t] = __uint_as_float(c_nf4_thresholds[t]);
     __syncthreads();
-    // Lane b holds bin b of the fast path's table: targets with int(t * kBinScale + 16) == b can only be
-    // decided by threshold bin_k (every other threshold is more than 1e-3 outside the bin), so the code is
-    // bin_k + (t >= T[bin_k]).  32 bins of width 1/16 over [-1, 1]; adjacent thresholds are >= 0.08 apart.
-    constexpr float kBinScale = 15.9999f;
-    const uint32_t bin_k = (uint32_t)(((t & 16) ? 0xEEEEDDDCCBBA9887ull : 0x6554432221110000ull) >> (4 * (t & 15))) & 15u;
-    const float bin_thr = s_thr[bin_k];
+    float bin_thr;
+    uint32_t bin_k;
+    nf4_bin_entry(t & 31, s_thr, bin_thr, bin_k);
 
 #pragma unroll 4
     for (int it = 0; it < 16384 / (8 * kQuantThreads); ++it) {
@@ -137,43 +191,8 @@ quantize_nf4_b64_kernel(const float *__restrict__ w, size_t n, size_t nb, uint8_
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
-        // Fast path: classify the approximate target ta = w * (1/absmax), which lies within 3e-7 of the exact
-        // quotient, against the one decision threshold its bin can reach.  If every ta of the thread stays at
-        // least 1e-6 away from its threshold, the exact quotient falls on the same side and the codes stand;
-        // otherwise (about one thread in 10^4) the eight codes are redone with the correctly rounded quotient.
-        const bool normal = am > 1e-30f && am < 1e30f;
-        float ra;
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(normal ? am : 1.0f));
-        uint32_t packed = 0;
-        float nearest = 1.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float ta = __fmul_rn(v[j], ra);
-            const int bin = __float2int_rz(__fmaf_rn(ta, kBinScale, 16.0f));  // NaN -> bin 0 -> code 0, as the scan
-            const float thr = __shfl_sync(0xffffffffu, bin_thr, bin);
-            const uint32_t k = __shfl_sync(0xffffffffu, bin_k, bin);
-            const float d = __fsub_rn(ta, thr);
-            nearest = fminf(nearest, fabsf(d));
-            packed |= (k + (d >= 0.0f ? 1u : 0u)) << (4 * j);
-        }
-        if (normal && nearest < 1e-6f) {
-            // target = w/absmax through the block's reciprocal: q = RN(w*rd), exact residual, one correction
-            // (Markstein) - correctly rounded whenever the quotient is a normal number, and every decision
-            // threshold is at |t| >= 0.0398, far above the range where it is not.
-            const float rd = __frcp_rn(am);
-            packed = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float q = __fmul_rn(v[j], rd);
-                const float t = __fmaf_rn(__fmaf_rn(-q, am, v[j]), rd, q);
-                packed |= nf4_code_bsearch(t, s_thr) << (4 * j);
-            }
-        } else if (!normal) {
-            // zero block (code 7), or an absmax at the ends of the exponent range / infinite: IEEE division
-            packed = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) packed |= nf4_code(v[j], am) << (4 * j);
-        }
+        bool redone;
+        uint32_t packed = nf4_pack8(v, am, bin_thr, bin_k, s_thr, redone);
         if (e0 + 8 > n) {  // ragged end: nibbles past the tensor stay 0 (odd-length padding included)
             const uint32_t valid = (e0 < n) ? (uint32_t)(n - e0) : 0u;
             packed = valid ? (packed & (0xFFFFFFFFu >> (4 * (8 - valid)))) : 0u;
@@ -493,6 +512,61 @@ __global__ void refresh_adapters_kernel(const RefreshBatch batch) {
     }
 }
 
+// ---- self-tests of the code selection (exhaustive parity sweeps; see the C ABI header) -------------
+// Codes of `count` consecutive fp32 bit patterns read as divided targets, two per output byte.
+__global__ void selftest_codes_of_targets_kernel(uint32_t first_bits, size_t count, uint8_t *__restrict__ out) {
+    for (size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x; 2 * b < count; b += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t lo = nf4_code_of_target(__uint_as_float(first_bits + (uint32_t)(2 * b)));
+        const uint32_t hi = (2 * b + 1 < count) ? nf4_code_of_target(__uint_as_float(first_bits + (uint32_t)(2 * b + 1))) : 0u;
+        out[b] = (uint8_t)(lo | (hi << 4));
+    }
+}
+
+// Every weight bit pattern in [first_bits, first_bits + count) against one block absmax: the quantise kernel's
+// own code selection (nf4_pack8: approximate quotient, 32-bin table, exact redo in the guard band) must give
+// the code of the IEEE quotient (nf4_code).  out[0] = weights whose codes differ, out[1] = threads that took
+// the exact redo, out[2] = the first differing bit pattern (if any).
+__global__ void __launch_bounds__(256)
+selftest_fast_path_kernel(float absmax, uint32_t first_bits, unsigned long long count, unsigned long long *out) {
+    __shared__ float s_thr[16];
+    if (threadIdx.x < 15) s_thr[threadIdx.x] = __uint_as_float(c_nf4_thresholds[threadIdx.x]);
+    __syncthreads();
+    float bin_thr;
+    uint32_t bin_k;
+    nf4_bin_entry(threadIdx.x & 31, s_thr, bin_thr, bin_k);
+    unsigned long long bad = 0, redo = 0, first_bad = ~0ull;
+    const unsigned long long groups = (count + 7) / 8, stride = (unsigned long long)gridDim.x * blockDim.x;
+    // whole warps iterate together (the table lives in the lanes); trailing groups are computed and discarded
+    const unsigned long long rounds = (groups + stride - 1) / stride;
+    for (unsigned long long r = 0; r < rounds; ++r) {
+        const unsigned long long g = r * stride + (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned long long i = g * 8 + j;
+            v[j] = i < count ? __uint_as_float(first_bits + (uint32_t)i) : 0.0f;
+        }
+        bool redone;
+        const uint32_t fast = nf4_pack8(v, absmax, bin_thr, bin_k, s_thr, redone);
+        if (g < groups) {
+            redo += redone ? 1u : 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const unsigned long long i = g * 8 + j;
+                if (i < count && ((fast >> (4 * j)) & 15u) != nf4_code(v[j], absmax)) {
+                    bad += 1;
+                    if (first_bad == ~0ull) first_bad = first_bits + (uint32_t)i;
+                }
+            }
+        }
+    }
+    if (bad) {
+        atomicAdd(out, bad);
+        atomicMin(out + 2, first_bad);
+    }
+    if (redo) atomicAdd(out + 1, redo);
+}
+
 inline unsigned grid_for(size_t work, unsigned per_block) { return (unsigned)((work + per_block - 1) / per_block); }
 
 }  // namespace
@@ -707,6 +781,25 @@ int launch_refresh_adapters(qlc_ctx *ctx, qlc_layer *const *layers, size_t n) {
         if (batch.n == kRefreshBatch) QLC_TRY(flush());
     }
     return flush();
+}
+
+int selftest_codes_of_targets(qlc_ctx *ctx, uint32_t first_bits, size_t count, uint8_t *d_out) {
+    if (count == 0) return QLC_OK;
+    const unsigned grid = (unsigned)ctx->sm_count * 8u;
+    selftest_codes_of_targets_kernel<<<grid, 256, 0, ctx->stream>>>(first_bits, count, d_out);
+    ctx->launches += 1;
+    QLC_CUDA(cudaGetLastError());
+    return QLC_OK;
+}
+
+int selftest_fast_path(qlc_ctx *ctx, float absmax, uint32_t first_bits, unsigned long long count,
+                       unsigned long long *d_out3) {
+    if (count == 0) return QLC_OK;
+    const unsigned grid = (unsigned)ctx->sm_count * 8u;
+    selftest_fast_path_kernel<<<grid, 256, 0, ctx->stream>>>(absmax, first_bits, count, d_out3);
+    ctx->launches += 1;
+    QLC_CUDA(cudaGetLastError());
+    return QLC_OK;
 }
 
 }  // namespace qlc

@@ -32,11 +32,13 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <atomic>
 #include <map>
 #include <new>
 
 #include "common.cuh"
 #include "nf4_decode.cuh"
+#include "ptx.cuh"
 
 namespace qlc {
 namespace {
@@ -120,91 +122,8 @@ struct GemmArgs {
     long long *timing;  // optional per-CTA clock64 stamps (diagnostics; null in normal operation)
 };
 
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns false if the kernel is unwinding (this or another wait expired).
-constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at B200 clocks; a healthy wait is microseconds
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                            DeviceStatus *status, int site) {
-    const long long t0 = clock64();
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if ((i & 255u) == 255u && clock64() - t0 > kWaitCycles) {
-            *abort_flag = 1;
-            if (atomicCAS(&status->code, 0, (int)kStatusWaitTimeout) == 0) {
-                status->where = site;
-                status->block = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-                status->detail = (int)parity;
-                __threadfence_system();
-            }
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          DeviceStatus *status, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, site);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with fp32 operands read as tf32 (8 contraction elements = 32 bytes per instruction).
+// ---- PTX wrappers specific to this file (the shared ones are in ptx.cuh) ---------------------------
+// Same as umma_bf16 with fp32 operands read as tf32 (8 contraction elements = 32 bytes per instruction).
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
     asm volatile(
@@ -216,61 +135,6 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-// After a wait ran out, the CTA must not give up its shared memory while a bulk copy it issued a moment earlier can
-// still land there: a bounded pause (about 100 us, far longer than a copy takes) before the CTA leaves.  Only ever
-// executed on the failure path.
-__device__ __forceinline__ void pause_after_abort(volatile int *abort_flag) {
-    if (*abort_flag) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < 200000) {
-        }
-    }
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first TMA use.
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
-}
-
-// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
-// 16-byte units, descriptor version 1, 128-byte swizzle.
-// layout: 2 = 128-byte swizzle of 16-byte chunks; 1 = 128-byte swizzle of 32-byte chunks, the layout an
-// MN-major operand of 32-bit elements (tf32) has to use.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                              uint32_t layout = 2) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;  // version
-    d |= (uint64_t)layout << 61;  // swizzle mode
-    return d;
-}
 
 // fp32 -> tf32 (10 mantissa bits), round to nearest, ties away from zero.
 __device__ __forceinline__ uint32_t tf32_rna(float x) {
@@ -279,19 +143,10 @@ __device__ __forceinline__ uint32_t tf32_rna(float x) {
     return u;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&t);
-}
-
 __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
-}
-__device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
@@ -803,42 +658,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_a
                  "r"(bytes)
                  : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __noinline__ bool mbar_wait2_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                             DeviceStatus *status, int site) {
-    const long long t0 = clock64();
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if ((i & 255u) == 255u && clock64() - t0 > kWaitCycles) {
-            *abort_flag = 1;
-            if (atomicCAS(&status->code, 0, (int)kStatusWaitTimeout) == 0) {
-                status->where = site;
-                status->block = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-                status->detail = (int)parity;
-                __threadfence_system();
-            }
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                           DeviceStatus *status, int site) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    return mbar_wait2_slow(bar, parity, abort_flag, status, site);
-}
 // TMA tile load issued by one CTA of a pair; the completion bytes are reported to `bar`, which may live in
 // the peer CTA's shared memory (cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
@@ -846,16 +665,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
-}
-// TMA tile store shared -> global (rows / columns outside the tensor are clipped).
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
-                 "r"(c0), "r"(c1)
-                 : "memory");
-}
-// Closes this thread's group of TMA stores and waits until their shared-memory source has been read.
-__device__ __forceinline__ void tma_store_commit_and_wait_read() {
-    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
@@ -1006,7 +815,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (uint32_t it = 0; it < total_steps; ++it) {
                 const int s = it % kStages2;
                 const uint32_t ph = (it / kStages2) & 1u;
-                if (!mbar_wait2(empty_bar(s), ph ^ 1u, abort_flag, args.status, 11)) break;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, 11)) break;
                 const bool ext = it >= main_steps;
                 const uint32_t a_dst = smem_base + s * kStageBytes2;
                 const uint32_t b_dst = a_dst + kABytes2;
@@ -1041,7 +850,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int s = it % kStages2;
                 const uint32_t ph = (it / kStages2) & 1u;
                 const long long tw = tstamp ? clock64() : 0;
-                if (!mbar_wait2(full_bar(s), ph, abort_flag, args.status, 12)) {
+                if (!mbar_wait(full_bar(s), ph, abort_flag, args.status, 12)) {
                     ok = false;
                     break;
                 }
@@ -1143,7 +952,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const float scale = args.dq ? __fmul_rn(s_q127[nraw & 255u], na2) : na2;
                 if (valid && it + 2 < main_steps) fetch(it + 2, nc, nraw, na2);
                 const long long tw = tstamp ? clock64() : 0;
-                if (!mbar_wait2(empty_bar(s), ph ^ 1u, abort_flag, args.status, 13)) break;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, 13)) break;
                 if (tstamp) prod_wait += clock64() - tw;
                 if (!ext) {
                     const uint32_t dst = smem_base + s * kStageBytes2 + kABytes2;
@@ -1231,7 +1040,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const float scale = args.dq ? __fmul_rn(s_q127[nraw & 255u], na2) : na2;
                 if (valid && it + 2 < main_steps) fetch(it + 2, nc, nraw, na2);
                 const long long tw = tstamp ? clock64() : 0;
-                if (!mbar_wait2(empty_bar(s), ph ^ 1u, abort_flag, args.status, 13)) break;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, 13)) break;
                 const long long td = tstamp ? clock64() : 0;
                 if (tstamp) {
                     prod_wait += td - tw;
@@ -1276,7 +1085,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
 
         // epilogue: this CTA's two 128x256 accumulators -> registers -> (bf16: shared memory -> TMA store)
-        if (mbar_wait2(tmem_full_bar, 0, abort_flag, args.status, 14)) {
+        if (mbar_wait(tmem_full_bar, 0, abort_flag, args.status, 14)) {
             tc_fence_after();
             if (tstamp && threadIdx.x == 64) tstamp[7] = clock64();
             const int quarter = warp & 3;
@@ -1311,7 +1120,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pieces_bar);
                 finish = false;
-                if (mbar_wait2(pieces_bar, 0, abort_flag, args.status, 15)) {
+                if (mbar_wait(pieces_bar, 0, abort_flag, args.status, 15)) {
                     if (threadIdx.x == 64) {
                         int *counter = args.counters + cut_tile * 2 + rank;
                         const int prev = atomicAdd(counter, 1);
@@ -1321,7 +1130,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         __threadfence();
                         mbar_arrive(verdict_bar);
                     }
-                    if (mbar_wait2(verdict_bar, 0, abort_flag, args.status, 16)) finish = *s_last != 0;
+                    if (mbar_wait(verdict_bar, 0, abort_flag, args.status, 16)) finish = *s_last != 0;
                 }
             }
             // One 32-column group of row (quarter * 32 + lane) of accumulator a.
@@ -1882,7 +1691,9 @@ int umma_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, size_t batch
 constexpr size_t kNoAllocMaxRows = 8192;
 static __device__ __align__(256) unsigned char g_forward_scratch[kNoAllocMaxRows * kRankPad * 2];
 constexpr int kMaxDevices = 64;
-static void *g_forward_scratch_addr[kMaxDevices];  // per device, filled on the first call on that device
+// per device, filled on the first call on that device; atomic because contexts of several host threads may
+// make their first call at the same time (they all store the same value)
+static std::atomic<void *> g_forward_scratch_addr[kMaxDevices];
 
 int umma_qlora_forward_noalloc(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *d_x, size_t batch, void *d_y) {
     if (batch > kNoAllocMaxRows)
@@ -1891,14 +1702,14 @@ int umma_qlora_forward_noalloc(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *
                     "%zu-byte device array); got %zu rows - split the batch or use qlc_qlora_forward_dev",
                     kNoAllocMaxRows, sizeof(g_forward_scratch), batch);
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(QLC_ERR_GPU, "device index %d out of range", ctx->device);
-    if (!g_forward_scratch_addr[ctx->device]) {
+    void *scratch = g_forward_scratch_addr[ctx->device].load(std::memory_order_acquire);
+    if (!scratch) {
         // one-time set-up for this device (the caller made it current): resolve the symbol's device address
-        void *p = nullptr;
-        QLC_CUDA(cudaGetSymbolAddress(&p, g_forward_scratch));
-        if (!p) return fail(QLC_ERR_GPU, "cudaGetSymbolAddress returned a null address");
-        g_forward_scratch_addr[ctx->device] = p;
+        QLC_CUDA(cudaGetSymbolAddress(&scratch, g_forward_scratch));
+        if (!scratch) return fail(QLC_ERR_GPU, "cudaGetSymbolAddress returned a null address");
+        g_forward_scratch_addr[ctx->device].store(scratch, std::memory_order_release);
     }
-    __nv_bfloat16 *t1p = static_cast<__nv_bfloat16 *>(g_forward_scratch_addr[ctx->device]);
+    __nv_bfloat16 *t1p = static_cast<__nv_bfloat16 *>(scratch);
     CUtensorMap tX, tT1, tB;
     QLC_TRY(make_map(&tX, d_x, batch, L->in_dim, 128));
     GemmArgs a = base_args(ctx, L);

@@ -15,8 +15,7 @@ from typing import List, Optional
 
 import numpy as np
 
-from . import (Adam8bit, AdamConfig, LoraAdapter, QloraLinear, QuantConfig, QuantizedTensor, NF4_LEVELS,
-               default_context)
+from . import Adam8bit, AdamConfig, LoraAdapter, QloraLinear, QuantConfig, QuantizedTensor
 
 __all__ = ["quantize_nf4", "qlora_linear_forward", "qlora_linear_backward", "QuantizedWeight", "BackwardOut",
            "PagedAdam"]
@@ -41,14 +40,14 @@ class QuantizedWeight:
         return list(self._codes)
 
     def dequantize(self) -> List[float]:
-        """lib.rs:58-70: NF4_LEVELS[code] * scales[idx / block_size], on the exported fields."""
-        n = self.rows * self.cols
-        c = np.frombuffer(self._codes, np.uint8)
-        nib = np.empty(2 * c.size, np.uint8)
-        nib[0::2] = c & 0x0F
-        nib[1::2] = c >> 4
-        s = np.repeat(np.asarray(self.scales, np.float32), self.block_size)[:n]
-        return (NF4_LEVELS[nib[:n]] * s).astype(np.float32).tolist()
+        """lib.rs:58-70: NF4_LEVELS[code] * scales[idx / block_size] on the exported fields (codes and decoded
+        fp32 scales), computed on the GPU: the fields are rebuilt into a device tensor exactly as the forward
+        and backward entry points do (lib.rs:181-188) and dequantised there (one fp32 multiply per element,
+        bit-identical to the reference's loop)."""
+        if len(self._codes) != (self.rows * self.cols + 1) // 2:
+            raise ValueError("QuantizedWeight codes length does not match rows*cols")
+        t = QuantizedTensor.from_raw_parts(self.rows, self.cols, self.block_size, self._codes, self.scales)
+        return t.dequantize().tolist()
 
     def __repr__(self) -> str:
         return (f"QuantizedWeight(rows={self.rows}, cols={self.cols}, block_size={self.block_size}, "
