@@ -369,7 +369,13 @@ int qlc_llama_destroy(qlc_llama *model);
  * NF4-quantised on the GPU (the reference quantises only adapter targets and keeps the others in fp32). */
 int qlc_llama_set_layer(qlc_llama *model, size_t layer, const float *attn_norm, const float *mlp_norm,
                         const float *const *weights, size_t block_size, int double_quant);
-/* a: (r, in), b: (out, r) of the adapter on projection `kind` (llama.rs:228-242). */
+/* Same, quantising only the projections with quantize[QLC_LLAMA_*] != 0; the others stay frozen fp32 matrices
+ * (Proj::Raw, llama.rs:87-93, 236-238: the reference quantises only adapter targets) and are multiplied as they
+ * are: in fp32 in the FP32_EXACT and TF32 modes, rounded to bf16 on the tensor-core path. */
+int qlc_llama_set_layer_mixed(qlc_llama *model, size_t layer, const float *attn_norm, const float *mlp_norm,
+                              const float *const *weights, const int *quantize, size_t block_size, int double_quant);
+/* a: (r, in), b: (out, r) of the adapter on projection `kind` (llama.rs:228-242).  A raw projection is quantised
+ * first (block 64, double quantisation: QuantConfig::default()), as the reference's loader does for targets. */
 int qlc_llama_attach_adapter(qlc_llama *model, size_t layer, int kind, const float *a, const float *b, size_t r,
                              float alpha);
 qlc_layer *qlc_llama_projection(qlc_llama *model, size_t layer, int kind);

@@ -100,6 +100,7 @@ SIGNATURES = {
     "qlc_llama_create": (_i, [_vp, _vp, _vp, _vp, _pp]),
     "qlc_llama_destroy": (_i, [_vp]),
     "qlc_llama_set_layer": (_i, [_vp, _sz, _vp, _vp, _vp, _sz, _i]),
+    "qlc_llama_set_layer_mixed": (_i, [_vp, _sz, _vp, _vp, _vp, _vp, _sz, _i]),
     "qlc_llama_attach_adapter": (_i, [_vp, _sz, _i, _vp, _vp, _sz, C.c_float]),
     "qlc_llama_projection": (_vp, [_vp, _sz, _i]),
     "qlc_llama_forward": (_i, [_vp, _vp, _sz, _sz, _vp]),

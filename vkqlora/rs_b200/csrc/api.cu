@@ -191,6 +191,30 @@ int layer_tf32_operands(qlc_layer *L) {
     return QLC_OK;
 }
 
+int layer_create_raw(qlc_ctx *ctx, const float *d_weight, size_t out_dim, size_t in_dim, qlc_layer **out) {
+    qlc_layer *L = new (std::nothrow) qlc_layer();
+    if (!L) return fail(QLC_ERR_GPU, "out of host memory");
+    L->ctx = ctx;
+    ctx->refs += 1;
+    L->in_dim = in_dim;
+    L->out_dim = out_dim;
+    const size_t n = out_dim * in_dim;
+    int st = QLC_OK;
+    if (cudaMalloc(reinterpret_cast<void **>(&L->d_w_raw), (n + 4) * 4) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void **>(&L->d_w_raw_bf16), (n + 8) * 2) != cudaSuccess)
+        st = fail(QLC_ERR_GPU, "out of device memory for a raw (%zu, %zu) projection", out_dim, in_dim);
+    if (st == QLC_OK && n &&
+        cudaMemcpyAsync(L->d_w_raw, d_weight, n * 4, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+        st = fail(QLC_ERR_GPU, "copy of the raw weight failed");
+    if (st == QLC_OK) st = launch_convert_f32_to_bf16(ctx, L->d_w_raw, L->d_w_raw_bf16, n);
+    if (st != QLC_OK) {
+        qlc_layer_destroy(L);
+        return st;
+    }
+    *out = L;
+    return QLC_OK;
+}
+
 }  // namespace qlc
 
 using namespace qlc;
@@ -698,6 +722,8 @@ int qlc_layer_destroy(qlc_layer *L) {
     cudaFree(L->d_b_pad32);
     cudaFree(L->d_bt_pad32);
     cudaFree(L->d_grad_bucket);
+    cudaFree(L->d_w_raw);
+    cudaFree(L->d_w_raw_bf16);
     qlc_qtensor_destroy(L->w);
     qlc_ctx_destroy(L->ctx);
     delete L;
@@ -780,23 +806,23 @@ int qlc_layer_grad_bucket(qlc_layer *L, float **d_bucket, size_t *n_floats) {
 // Handles are bound to the device they were created on: a layer of another GPU's context would make this
 // GPU's kernels dereference foreign device pointers.
 static int same_device(const qlc_ctx *ctx, const qlc_layer *L) {
-    if (L->ctx->device != ctx->device || L->w->device != ctx->device)
-        return fail(QLC_ERR_GPU, "layer lives on device %d (weight on %d), context on %d", L->ctx->device, L->w->device,
-                    ctx->device);
+    const int wdev = L->w ? L->w->device : L->ctx->device;
+    if (L->ctx->device != ctx->device || wdev != ctx->device)
+        return fail(QLC_ERR_GPU, "layer lives on device %d (weight on %d), context on %d", L->ctx->device, wdev, ctx->device);
     return QLC_OK;
 }
 
 // Which arithmetic a call uses (see QLC_PRECISION_* in the header).
 static int pick_path(qlc_ctx *ctx, const qlc_layer *L, bool *use_umma) {
     const bool ok = umma_supported(L);
-    if (ctx->precision == QLC_PRECISION_FP32_EXACT) {
-        *use_umma = false;
+    if (ctx->precision == QLC_PRECISION_FP32_EXACT || (!L->w && ctx->precision == QLC_PRECISION_TF32)) {
+        *use_umma = false;  // (a raw projection has no tf32 kernels: TF32 mode multiplies it in exact fp32)
     } else if (ctx->precision == QLC_PRECISION_BF16 || ctx->precision == QLC_PRECISION_TF32) {
         if (!ok)
             return fail(QLC_ERR_GPU,
                         "tensor-core path needs block_size 32, 64, 128 or 256, in_dim/out_dim multiples of 64 and rank <= 64 "
                         "(got block %zu, in %zu, out %zu, r %zu)",
-                        L->w->block_size, L->in_dim, L->out_dim, L->r);
+                        L->w ? L->w->block_size : (size_t)0, L->in_dim, L->out_dim, L->r);
         *use_umma = true;
     } else {
         *use_umma = ok;
@@ -857,11 +883,11 @@ int qlc_qlora_forward_dev_noalloc(qlc_ctx *ctx, qlc_layer *L, const void *d_x, s
     QLC_TRY(same_device(ctx, L));
     if (batch == 0 || L->out_dim == 0) return QLC_OK;
     if (!d_x || !d_y) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
-    if (!umma_supported(L))
+    if (!L->w || !umma_supported(L))
         return fail(QLC_ERR_INVALID_CONFIG,
                     "qlc_qlora_forward_dev_noalloc needs a tensor-core-eligible layer (block_size 32, 64, 128 or 256, in_dim and "
                     "out_dim multiples of 64, rank <= 64); got block %zu, in %zu, out %zu, r %zu",
-                    L->w->block_size, L->in_dim, L->out_dim, L->r);
+                    L->w ? L->w->block_size : (size_t)0, L->in_dim, L->out_dim, L->r);
     QLC_CUDA(cudaSetDevice(ctx->device));
     return umma_qlora_forward_noalloc(ctx, L, static_cast<const __nv_bfloat16 *>(d_x), batch, d_y);
 }

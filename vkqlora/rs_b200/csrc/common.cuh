@@ -105,7 +105,11 @@ struct qlc_qtensor {
 
 struct qlc_layer {
     qlc_ctx *ctx = nullptr;
-    qlc_qtensor *w = nullptr;
+    qlc_qtensor *w = nullptr;  // null for a raw (unquantised) projection, which the model code creates
+    // Raw projection (qlora-model/src/llama.rs:87-93, Proj::Raw): the frozen (out_dim, in_dim) weight as fp32
+    // (exact and TF32 modes) and rounded to bf16 (tensor-core path).  Never has an adapter.
+    float *d_w_raw = nullptr;
+    __nv_bfloat16 *d_w_raw_bf16 = nullptr;
     size_t in_dim = 0, out_dim = 0, r = 0;
     float alpha = 0.f;
     float *d_a = nullptr;  // (r, in_dim) fp32
@@ -214,6 +218,8 @@ int ctx_pinned(qlc_ctx *ctx, size_t bytes, void **out);
 int ctx_io(qlc_ctx *ctx, size_t bytes, void **out);
 int ctx_tile_counters(qlc_ctx *ctx, int set, size_t count, int **out);
 int layer_tf32_operands(qlc_layer *layer);
+// A layer that multiplies by a plain (out_dim, in_dim) fp32 device matrix, copied; no quantisation, no adapter.
+int layer_create_raw(qlc_ctx *ctx, const float *d_weight, size_t out_dim, size_t in_dim, qlc_layer **out);
 // Event bracketing of a launch when profiling is enabled (no-ops otherwise).
 void prof_begin(qlc_ctx *ctx, int slot, cudaStream_t stream = nullptr);
 void prof_end(qlc_ctx *ctx, cudaStream_t stream = nullptr);

@@ -134,6 +134,8 @@ int exact_matmul_trans_a(qlc_ctx *ctx, const float *a, const float *b, size_t m,
 
 // QloraLinear::forward (qlora.rs:86-107) in the reference's exact order.
 int exact_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const float *x, size_t batch, float *y) {
+    // raw projection: Y = X·W^T on the fp32 weight (qlora-model/src/llama.rs:101-105)
+    if (!L->w) return exact_matmul_trans_b(ctx, x, L->d_w_raw, batch, L->in_dim, L->out_dim, y);
     const qlc_qtensor *q = L->w;
     const size_t in = L->in_dim, out = L->out_dim, r = L->r;
     const size_t b_scales = align256(q->nb * 4), b_t1 = align256(batch * r * 4), b_t2 = align256(batch * out * 4);
@@ -159,6 +161,8 @@ int exact_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const float *x, size_t batch
 // QloraLinear::backward (qlora.rs:116-165) in the reference's exact order.
 int exact_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const float *x, const float *dy, size_t batch, float *gx,
                          float *ga, float *gb) {
+    // raw projection: dX = dY·W (qlora-model/src/llama.rs:119-123)
+    if (!L->w) return exact_matmul(ctx, dy, L->d_w_raw, batch, L->out_dim, L->in_dim, gx);
     const qlc_qtensor *q = L->w;
     const size_t in = L->in_dim, out = L->out_dim, r = L->r;
     const size_t b_scales = align256(q->nb * 4), b_dys = align256(batch * out * 4), b_t1 = align256(batch * r * 4),

@@ -1503,8 +1503,10 @@ int qlc_llama_destroy(qlc_llama *m) {
     return qlc_ctx_destroy(ctx);
 }
 
-int qlc_llama_set_layer(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
-                        const float *const *weights, size_t block_size, int double_quant) {
+// quantize == nullptr: every projection is NF4-quantised; otherwise projection k is quantised iff quantize[k] != 0
+// and kept as a raw fp32 matrix (llama.rs:87-93, Proj::Raw) otherwise.
+static int set_layer_impl(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
+                          const float *const *weights, const int *quantize, size_t block_size, int double_quant) {
     if (!m || !attn_norm || !mlp_norm || !weights) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
     if (li >= m->layers.size()) return fail(QLC_ERR_INVALID_CONFIG, "layer %zu of %zu", li, m->layers.size());
     QLC_CUDA(cudaSetDevice(m->ctx->device));
@@ -1518,12 +1520,35 @@ int qlc_llama_set_layer(qlc_llama *m, size_t li, const float *attn_norm, const f
         if (!weights[k]) return fail(QLC_ERR_INVALID_CONFIG, "null weight matrix %d", k);
         const size_t o = proj_out(m, k), i = proj_in(m, k);
         qlc_layer *nl = nullptr;
-        QLC_TRY(qlc_layer_create_from_fp32(m->ctx, weights[k], o * i, o, i, block_size, double_quant, nullptr, 0, nullptr, 0, 0,
-                                           0.0f, &nl));
+        if (!quantize || quantize[k]) {
+            QLC_TRY(qlc_layer_create_from_fp32(m->ctx, weights[k], o * i, o, i, block_size, double_quant, nullptr, 0, nullptr,
+                                               0, 0, 0.0f, &nl));
+        } else {
+            float *tmp = nullptr;
+            QLC_CUDA(cudaMalloc(reinterpret_cast<void **>(&tmp), (o * i + 4) * 4));
+            int st = QLC_OK;
+            if (cudaMemcpyAsync(tmp, weights[k], o * i * 4, cudaMemcpyHostToDevice, m->ctx->stream) != cudaSuccess)
+                st = fail(QLC_ERR_GPU, "upload of weight matrix %d failed", k);
+            if (st == QLC_OK) st = layer_create_raw(m->ctx, tmp, o, i, &nl);
+            cudaStreamSynchronize(m->ctx->stream);
+            cudaFree(tmp);
+            QLC_TRY(st);
+        }
         qlc_layer_destroy(L.proj[k]);
         L.proj[k] = nl;
     }
     return QLC_OK;
+}
+
+int qlc_llama_set_layer(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
+                        const float *const *weights, size_t block_size, int double_quant) {
+    return set_layer_impl(m, li, attn_norm, mlp_norm, weights, nullptr, block_size, double_quant);
+}
+
+int qlc_llama_set_layer_mixed(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
+                              const float *const *weights, const int *quantize, size_t block_size, int double_quant) {
+    if (!quantize) return fail(QLC_ERR_INVALID_CONFIG, "null quantize flags");
+    return set_layer_impl(m, li, attn_norm, mlp_norm, weights, quantize, block_size, double_quant);
 }
 
 int qlc_llama_attach_adapter(qlc_llama *m, size_t li, int kind, const float *a, const float *b, size_t r, float alpha) {
@@ -1534,7 +1559,18 @@ int qlc_llama_attach_adapter(qlc_llama *m, size_t li, int kind, const float *a, 
     if (!old) return fail(QLC_ERR_INVALID_CONFIG, "set the layer's weights before attaching adapters");
     const size_t o = proj_out(m, kind), i = proj_in(m, kind);
     qlc_layer *nl = nullptr;
-    QLC_TRY(qlc_layer_create(m->ctx, qlc_layer_weight(old), a, r * i, b, o * r, r, alpha, &nl));
+    if (old->w) {
+        QLC_TRY(qlc_layer_create(m->ctx, qlc_layer_weight(old), a, r * i, b, o * r, r, alpha, &nl));
+    } else {
+        // A raw projection that becomes an adapter target is quantised now, with the reference's default
+        // QuantConfig (block 64, double quantisation), as its loader does for targets (llama.rs:228-249).
+        QLC_CUDA(cudaSetDevice(m->ctx->device));
+        qlc_qtensor *q = nullptr;
+        QLC_TRY(qlc_quantize_nf4_dev(m->ctx, old->d_w_raw, o, i, 64, 1, &q));
+        const int st = qlc_layer_create(m->ctx, q, a, r * i, b, o * r, r, alpha, &nl);
+        qlc_qtensor_destroy(q);  // the layer holds its own reference on success
+        QLC_TRY(st);
+    }
     qlc_layer_destroy(old);
     m->layers[li].proj[kind] = nl;
     return QLC_OK;

@@ -1522,6 +1522,9 @@ bool pdl_enabled() {
 }
 
 bool umma_supported(const qlc_layer *L) {
+    if (!L->w)  // raw projection: plain bf16 GEMMs, both operands by TMA
+        return L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
+               L->in_dim < (1u << 30) && L->out_dim < (1u << 30);
     const qlc_qtensor *q = L->w;
     const bool block_ok = q->block_size == 32 || q->block_size == 64 || q->block_size == 128 || q->block_size == 256;
     return block_ok && L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
@@ -1647,6 +1650,11 @@ static int token_contract(qlc_ctx *ctx, qlc_layer *L, size_t batch, const Contra
 // d_x: (batch, in_dim) bf16, or fp32 when tf32.
 int umma_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, size_t batch, void *d_y, int y_dtype, bool tf32) {
     if (batch >= (1u << 31) / 2) return fail(QLC_ERR_GPU, "batch too large for the tensor-core path");
+    if (!L->w) {  // raw projection: Y = X·W^T with the bf16 copy of the weight
+        if (tf32) return fail(QLC_ERR_GPU, "internal: raw projections have no tf32 path");
+        return umma_gemm_bf16(ctx, static_cast<const __nv_bfloat16 *>(d_x), L->d_w_raw_bf16, false, d_y, batch, L->out_dim,
+                              L->in_dim, y_dtype == QLC_DTYPE_BF16);
+    }
     if (tf32 && !use_paired_ctas()) return fail(QLC_ERR_GPU, "the TF32 mode needs the paired-CTA kernel");
     if (tf32) QLC_TRY(layer_tf32_operands(L));
     const size_t es = tf32 ? 4 : 2, step = tf32 ? 32 : 64;
@@ -1740,6 +1748,11 @@ int umma_qlora_forward_noalloc(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *
 int umma_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, const void *d_dy, size_t batch, void *d_gx,
                         int gx_dtype, float *d_ga, float *d_gb, int accumulate, bool tf32) {
     if (batch >= (1u << 31) / 2) return fail(QLC_ERR_GPU, "batch too large for the tensor-core path");
+    if (!L->w) {  // raw projection: dX = dY·W with the bf16 copy of the weight; no adapter, no adapter gradients
+        if (tf32) return fail(QLC_ERR_GPU, "internal: raw projections have no tf32 path");
+        return umma_gemm_bf16(ctx, static_cast<const __nv_bfloat16 *>(d_dy), L->d_w_raw_bf16, true, d_gx, batch, L->in_dim,
+                              L->out_dim, gx_dtype == QLC_DTYPE_BF16);
+    }
     if (tf32 && !use_paired_ctas()) return fail(QLC_ERR_GPU, "the TF32 mode needs the paired-CTA kernel");
     if (tf32) QLC_TRY(layer_tf32_operands(L));
     const size_t es = tf32 ? 4 : 2, step = tf32 ? 32 : 64;

@@ -68,8 +68,11 @@ class LlamaModel:
         check(lib.qlc_llama_create(self._ctx._h, C.byref(c), e.ctypes.data, n.ctypes.data, C.byref(h)))
         self._h = h
 
-    def set_layer(self, li: int, attn_norm, mlp_norm, weights: Dict[str, np.ndarray], quant: QuantConfig = QuantConfig()) -> None:
-        """weights[kind]: (out, in) fp32, all seven kinds (llama.rs:250-297)."""
+    def set_layer(self, li: int, attn_norm, mlp_norm, weights: Dict[str, np.ndarray], quant: QuantConfig = QuantConfig(),
+                  quantize: Optional[Sequence[str]] = None) -> None:
+        """weights[kind]: (out, in) fp32, all seven kinds (llama.rs:250-297).  quantize=None: every projection is
+        NF4-quantised.  quantize=("q", "v"): only those kinds are; the others stay raw fp32 matrices, as in the
+        reference, which quantises adapter targets only (llama.rs:228-249)."""
         mats = []
         for k in KINDS:
             o, i = self.cfg.proj_dims(k)
@@ -79,7 +82,13 @@ class LlamaModel:
             mats.append(w)
         ptrs = (C.c_void_p * 7)(*[m.ctypes.data for m in mats])
         an, mn = _f32(attn_norm), _f32(mlp_norm)
-        check(lib.qlc_llama_set_layer(self._h, li, an.ctypes.data, mn.ctypes.data, ptrs, quant.block_size, int(quant.double_quant)))
+        if quantize is None:
+            check(lib.qlc_llama_set_layer(self._h, li, an.ctypes.data, mn.ctypes.data, ptrs, quant.block_size,
+                                          int(quant.double_quant)))
+        else:
+            flags = (C.c_int * 7)(*[int(k in quantize) for k in KINDS])
+            check(lib.qlc_llama_set_layer_mixed(self._h, li, an.ctypes.data, mn.ctypes.data, ptrs, flags, quant.block_size,
+                                                int(quant.double_quant)))
 
     def attach_adapter(self, li: int, kind: str, a, b, rank: int, alpha: float) -> None:
         a, b = _f32(a).reshape(-1), _f32(b).reshape(-1)
