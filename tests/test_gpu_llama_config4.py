@@ -98,9 +98,10 @@ def test_config4_width_exact_and_bf16(v, layers):
         assert worst[k] <= bound, (k, worst[k], bound)
 
 
-# relative Frobenius error of the bf16 mode against the fp32 oracle, by number of layers
-BF16_BOUNDS = {1: {"logits": 2e-2, "grad_a": 5e-2, "grad_b": 5e-2},
-               2: {"logits": 2e-2, "grad_a": 5e-2, "grad_b": 5e-2}}
+# Relative Frobenius error of the bf16 mode against the fp32 oracle, by number of layers.  Measured on a B200:
+# 1 layer: logits 4.49e-3, grad_a 8.70e-3, grad_b 8.97e-3; 2 layers: logits 6.05e-3, grad_a 1.22e-2, grad_b 1.22e-2.
+BF16_BOUNDS = {1: {"logits": 8.9e-3, "grad_a": 1.7e-2, "grad_b": 1.79e-2},
+               2: {"logits": 1.2e-2, "grad_a": 2.4e-2, "grad_b": 2.4e-2}}
 
 
 def test_reference_qv_configuration_other_projections_raw(v):
