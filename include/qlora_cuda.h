@@ -85,6 +85,12 @@ int qlc_ctx_set_precision(qlc_ctx *ctx, int precision);
 int qlc_ctx_synchronize(qlc_ctx *ctx);
 /* The context's cudaStream_t, for callers that interleave their own work. */
 void *qlc_ctx_stream(qlc_ctx *ctx);
+/* Copies between host memory and device memory in the context's stream order (asynchronous for pinned host
+ * memory; complete after qlc_ctx_synchronize), for hosts that link no CUDA runtime of their own - e.g. to read
+ * a layer's device gradient bucket (qlc_layer_grad_bucket) after an all-reduce.  (No counterpart in the
+ * reference: its buffers never outlive a call.) */
+int qlc_ctx_copy_to_host(qlc_ctx *ctx, void *dst, const void *d_src, size_t bytes);
+int qlc_ctx_copy_to_device(qlc_ctx *ctx, void *d_dst, const void *src, size_t bytes);
 /* Number of kernels this context has launched since creation (diagnostics / benchmarks). */
 uint64_t qlc_ctx_launch_count(const qlc_ctx *ctx);
 
@@ -213,6 +219,24 @@ int qlc_qlora_backward(qlc_ctx *ctx, qlc_layer *layer, const float *x, size_t x_
 int qlc_qlora_forward_host(qlc_ctx *ctx, qlc_layer *layer, const void *x, int dtype, size_t batch, void *y);
 int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *layer, const void *x, const void *dy, int dtype, size_t batch,
                             void *grad_x, float *grad_a, float *grad_b);
+/* Forward and backward of one batch in one call, for callers that hold X and dY together (a benchmark step, or
+ * a backward pass replayed with a stored upstream gradient): the same results as qlc_qlora_forward_host followed
+ * by qlc_qlora_backward_host, but X crosses the host link once instead of twice and one row-slab pipeline
+ * (copy in | forward + backward | copy out) serves both passes.  The reference's two stateless calls upload X
+ * twice (qlora-wgpu/src/kernels.rs:262-267 and 301-307 each take x); those calls remain.  grad_a / grad_b may be
+ * NULL: the gradients then stay in the layer's device bucket (qlc_layer_grad_bucket), e.g. for an all-reduce. */
+int qlc_qlora_forward_backward_host(qlc_ctx *ctx, qlc_layer *layer, const void *x, const void *dy, int dtype,
+                                    size_t batch, void *y, void *grad_x, float *grad_a, float *grad_b);
+/* The same call without waiting: it returns once the copies and kernels are queued and hands out a ticket;
+ * qlc_ctx_wait(ctx, ticket) blocks until that submission's outputs are in host memory (qlc_ctx_synchronize
+ * waits for all of them and reports any kernel status).  A caller that keeps two submissions in flight, each with
+ * its own host buffers, hides the start and the end of one step's copies behind the other's: the host link stays
+ * busy in both directions.  Every host buffer of a submission must stay valid and untouched until its ticket has
+ * been waited for.  Shapes the pipeline does not take (see above) run synchronously and return a finished ticket. */
+int qlc_qlora_forward_backward_host_async(qlc_ctx *ctx, qlc_layer *layer, const void *x, const void *dy, int dtype,
+                                          size_t batch, void *y, void *grad_x, float *grad_a, float *grad_b,
+                                          uint64_t *ticket);
+int qlc_ctx_wait(qlc_ctx *ctx, uint64_t ticket);
 /* Device-pointer variants: activations (x, dy, y, grad_x) are `dtype`; d_grad_a / d_grad_b are
  * fp32 device buffers (may be NULL).  Asynchronous on the context's stream. */
 int qlc_qlora_forward_dev(qlc_ctx *ctx, qlc_layer *layer, const void *d_x, int dtype, size_t batch, void *d_y);
@@ -419,6 +443,16 @@ int qlc_selftest_nf4_codes_of_targets(qlc_ctx *ctx, uint32_t first_bits, size_t 
  * pattern. */
 int qlc_selftest_nf4_fast_path(qlc_ctx *ctx, float absmax, uint32_t first_bits, uint64_t count, uint64_t *mismatches,
                                uint64_t *redone, uint32_t *first_mismatch_bits);
+/* The exact Adam kernel computes its per-element square roots and its division with branch-free sequences
+ * (hardware approximation + exact FMA residual corrections) when all operands lie in the middle of the exponent
+ * range, and with the IEEE intrinsics otherwise.  This compares the two on the device:
+ *   which == 0: the square-root sequence against the IEEE square root for the `count` fp32 bit patterns from
+ *               `first_bits` (the kernel uses it for values in [2^-80, 2^80]; the tests sweep all of them);
+ *   which == 1: the division sequence against IEEE division for `count` operand pairs from a seeded generator
+ *               covering the kernel's operand windows (|numerator| in [2^-70, 2^70], denominator in [2^-40, 2^41]).
+ * Returns the number of differing results (must be 0) and the index of the first. */
+int qlc_selftest_adam_math(qlc_ctx *ctx, int which, uint32_t first_bits, uint64_t count, uint64_t seed,
+                           uint64_t *mismatches, uint64_t *first_mismatch);
 /* Failure-path test: enqueues a one-CTA kernel (no TMA, no tensor memory) whose thread 0 waits, with the
  * bounded wait of the tensor-core kernels, on an mbarrier nobody arrives on.  After `limit_cycles` SM clock
  * cycles (1 .. 1e8) the wait gives up, stores (code 1, site 99, block 0) in the context's status word and the

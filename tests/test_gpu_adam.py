@@ -253,3 +253,43 @@ def test_full_size_config3_bitwise(v, oracle):
             assert np.array_equal(st["m_codes"], os_["m_codes"]) and np.array_equal(st["v_codes"], os_["v_codes"])
             assert np.array_equal(st["m_scales"].view(np.uint32), os_["m_scales"].view(np.uint32))
             assert np.array_equal(st["v_scales"].view(np.uint32), os_["v_scales"].view(np.uint32))
+
+
+def test_branch_free_sqrt_and_div_equal_the_ieee_operations(v):
+    """The exact kernel's straight-line square root and division must round like IEEE sqrt and division wherever
+    the kernel uses them: the square root is swept over EVERY fp32 value in [2^-101, 2^101) (the kernel's window is
+    [2^-80, 2^80]), the division over 2^33 seeded operand pairs spanning its operand windows."""
+    import ctypes as C
+
+    from vkqlora.rs_b200 import _lib
+
+    ctx = v.GpuContext(0)
+    bad, first = C.c_uint64(), C.c_uint64()
+    lo, hi = (127 - 101) << 23, (127 + 101) << 23
+    _lib.check(_lib.lib.qlc_selftest_adam_math(ctx._h, 0, lo, hi - lo, 0, C.byref(bad), C.byref(first)))
+    assert bad.value == 0, (bad.value, hex(lo + first.value))
+    for seed in (1, 2):
+        _lib.check(_lib.lib.qlc_selftest_adam_math(ctx._h, 1, 0, 1 << 32, seed << 40, C.byref(bad), C.byref(first)))
+        assert bad.value == 0, (seed, bad.value, first.value)
+
+
+def test_adam_bitwise_outside_the_fast_windows(v, oracle):
+    """Gradients and state that leave the branch-free path's operand windows (tiny, huge, zero, mixed within one
+    thread's eight elements) and step constants outside its windows: the kernel must fall back to the IEEE
+    operations and stay bit-identical to the oracle."""
+    n = 8192
+    rng = np.random.default_rng(21)
+    scales = np.float32(10.0) ** rng.integers(-30, 20, n).astype(np.float32)   # per-element magnitudes 1e-30 .. 1e19
+    for cfg in (dict(), dict(lr=1e-12), dict(eps=2000.0), dict(beta2=0.9999999)):
+        opt, oopt = v.Adam8bit(v.AdamConfig(**cfg)), oracle.Adam8bit(**cfg)
+        p1 = [normal(70, n, 0.01)]
+        p2 = [p1[0].copy()]
+        for t in range(4):
+            g = (normal(700 + t, n, 1.0) * scales).astype(np.float32)
+            g[rng.integers(0, n, n // 8)] = 0.0
+            if t == 2:
+                g[:] = 0.0          # a whole step without gradient
+            opt.step(p1, [g])
+            oopt.step(p2, [g])
+            assert np.array_equal(p1[0].view(np.uint32), p2[0].view(np.uint32)), (cfg, t)
+        _compare_state(opt, oopt, 0)

@@ -259,6 +259,89 @@ def test_host_entry_points_pipelined_slabs_match_single_device_call(v, oracle, t
     _assert_close("grad_b", gb, gb_ref, out_dim, r)
 
 
+@pytest.mark.parametrize("batch", [700, 5120 + 300])
+def test_fused_forward_backward_host_equals_the_two_stateless_calls(v, oracle, tc_ctx, batch):
+    """qlc_qlora_forward_backward_host uploads X once and runs forward and backward slab by slab in one pipeline
+    (5420 rows), or falls back to the two calls (700 rows: below the slab threshold).  Y and dX must be
+    bit-identical to qlc_qlora_forward_host + qlc_qlora_backward_host; grad_A / grad_B (fp32 sums over slabs in the
+    same order) as well; and everything agrees with the oracle."""
+    from vkqlora.rs_b200 import _lib
+    out_dim, in_dim, r = 320, 256, 8
+    layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, seed=44)
+    xb, dyb = to_bf16_bits(x), to_bf16_bits(dy)
+    y2 = layer.forward_host(xb, batch, v.DTYPE_BF16)
+    gx2 = np.empty(batch * in_dim, np.uint16)
+    ga2, gb2 = np.empty(r * in_dim, np.float32), np.empty(out_dim * r, np.float32)
+    _lib.check(_lib.lib.qlc_qlora_backward_host(tc_ctx._h, layer._h, xb.ctypes.data, dyb.ctypes.data, v.DTYPE_BF16, batch,
+                                                gx2.ctypes.data, ga2.ctypes.data, gb2.ctypes.data))
+    y1, g1 = layer.forward_backward_host(xb, dyb, batch, v.DTYPE_BF16)
+    assert np.array_equal(y1, y2) and np.array_equal(g1.grad_x, gx2)
+    assert np.array_equal(g1.grad_a, ga2) and np.array_equal(g1.grad_b, gb2)
+    y_ref = oracle.qlora_forward(x, batch, wd, out_dim, in_dim, a, b, r, alpha, threads=8)
+    gx_ref, ga_ref, gb_ref = oracle.qlora_backward(x, dy, batch, wd, out_dim, in_dim, a, b, r, alpha, threads=8)
+    _assert_close("forward", bf16_bits_to_f32(y1), y_ref, batch, out_dim)
+    _assert_close("grad_x", bf16_bits_to_f32(g1.grad_x), gx_ref, batch, in_dim)
+    _assert_close("grad_a", g1.grad_a, ga_ref, r, in_dim)
+    _assert_close("grad_b", g1.grad_b, gb_ref, out_dim, r)
+    # gradients may stay on the device (NULL host pointers): the layer's bucket then holds them
+    y3, gx3 = np.empty_like(y1), np.empty_like(gx2)
+    _lib.check(_lib.lib.qlc_qlora_forward_backward_host(tc_ctx._h, layer._h, xb.ctypes.data, dyb.ctypes.data, v.DTYPE_BF16,
+                                                        batch, y3.ctypes.data, gx3.ctypes.data, None, None))
+    ptr, n = layer.grad_bucket()
+    assert n == r * (in_dim + out_dim)
+    got = np.empty(n, np.float32)
+    tc_ctx.copy_to_host(got.ctypes.data, ptr, 4 * n)
+    tc_ctx.synchronize()
+    assert np.array_equal(got[:r * in_dim], ga2) and np.array_equal(got[r * in_dim:], gb2)
+    assert np.array_equal(y3, y1) and np.array_equal(gx3, gx2)
+
+
+def test_async_fused_host_calls_two_in_flight(v, oracle, tc_ctx):
+    """qlc_qlora_forward_backward_host_async: three submissions with different inputs, two in flight at a time
+    (each with its own pinned host buffers), waited for by ticket.  Every result equals the synchronous call's:
+    a submission must not overwrite staged inputs or outputs that its predecessor still needs."""
+    import torch
+    out_dim, in_dim, r, batch = 320, 256, 8, 5120 + 300
+    layer, wd, x0, dy0, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, seed=46)
+    cases = []
+    for i in range(3):
+        x, dy = to_bf16_bits(normal(460 + i, batch * in_dim)), to_bf16_bits(normal(470 + i, batch * out_dim))
+        y, g = layer.forward_backward_host(x, dy, batch, v.DTYPE_BF16)
+        cases.append((x, dy, y, g))
+    pin = lambda n, dt: torch.empty(n, dtype=dt).pin_memory()
+    sets = [dict(x=pin(batch * in_dim, torch.int16), dy=pin(batch * out_dim, torch.int16), y=pin(batch * out_dim, torch.int16),
+                 gx=pin(batch * in_dim, torch.int16), ga=pin(r * in_dim, torch.float32), gb=pin(out_dim * r, torch.float32))
+            for _ in range(2)]
+    tickets, results = [None, None], []
+
+    def collect(k, i):
+        tc_ctx.wait(tickets[k])
+        s = sets[k]
+        results.append((i, s["y"].numpy().copy().view(np.uint16), s["gx"].numpy().copy().view(np.uint16),
+                        s["ga"].numpy().copy(), s["gb"].numpy().copy()))
+
+    for i, (x, dy, _, _) in enumerate(cases):
+        k = i & 1
+        if tickets[k] is not None:
+            collect(k, i - 2)
+        s = sets[k]
+        s["x"].numpy()[:] = x.view(np.int16)
+        s["dy"].numpy()[:] = dy.view(np.int16)
+        tickets[k] = layer.forward_backward_host_async(s["x"].data_ptr(), s["dy"].data_ptr(), batch, v.DTYPE_BF16,
+                                                       s["y"].data_ptr(), s["gx"].data_ptr(), s["ga"].data_ptr(),
+                                                       s["gb"].data_ptr())
+    collect(1, 1)
+    collect(0, 2)
+    tc_ctx.synchronize()
+    assert sorted(i for i, *_ in results) == [0, 1, 2]
+    for i, y, gx, ga, gb in results:
+        _, _, y_ref, g_ref = cases[i]
+        assert np.array_equal(y, y_ref) and np.array_equal(gx, g_ref.grad_x), i
+        assert np.array_equal(ga, g_ref.grad_a) and np.array_equal(gb, g_ref.grad_b), i
+    with pytest.raises(v.InvalidConfig):
+        tc_ctx.wait(10**6)
+
+
 @pytest.mark.parametrize("out_dim,in_dim", [(11008, 4096), (4096, 11008)])
 def test_tensor_core_projection_stack_shapes_rank64(v, oracle, tc_ctx, out_dim, in_dim):
     """BASELINE config 5 shapes (gate/up 11008x4096, down 4096x11008; r=64, alpha=128): 43 column tiles

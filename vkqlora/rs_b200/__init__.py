@@ -87,6 +87,17 @@ class GpuContext:
         check(lib.qlc_ctx_profile_read(self._h, slot, C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
+    def wait(self, ticket: int) -> None:
+        """Blocks until the asynchronous host-buffer submission `ticket` has delivered its outputs."""
+        check(lib.qlc_ctx_wait(self._h, ticket))
+
+    def copy_to_host(self, dst: int, d_src: int, nbytes: int) -> None:
+        """Device -> host copy in the context's stream order (complete after synchronize())."""
+        check(lib.qlc_ctx_copy_to_host(self._h, dst, d_src, nbytes))
+
+    def copy_to_device(self, d_dst: int, src: int, nbytes: int) -> None:
+        check(lib.qlc_ctx_copy_to_device(self._h, d_dst, src, nbytes))
+
     @property
     def stream(self) -> int:
         return int(lib.qlc_ctx_stream(self._h) or 0)
@@ -360,6 +371,31 @@ class QloraLinear:
         y = np.empty(batch * self.out_dim(), es)
         check(lib.qlc_qlora_forward_host(self._ctx._h, self._h, _p(x), dtype, batch, _p(y)))
         return y
+
+    def forward_backward_host(self, x: np.ndarray, dy: np.ndarray, batch: int, dtype: int):
+        """Forward and backward of one batch in one call (X crosses the host link once): returns (y, QloraGrads).
+        Host buffers in `dtype` (bf16 as uint16 bit patterns); copies are part of the call."""
+        es = np.uint16 if dtype == DTYPE_BF16 else np.float32
+        x = np.ascontiguousarray(x, dtype=es).reshape(-1)
+        dy = np.ascontiguousarray(dy, dtype=es).reshape(-1)
+        if x.size != batch * self.in_dim() or dy.size != batch * self.out_dim():
+            raise ShapeMismatch(_lib.ERR_SHAPE_MISMATCH, "shape mismatch: x must hold batch*in_dim and dy batch*out_dim values")
+        r = self._adapter.rank() if self._adapter else 0
+        y, gx = np.empty(batch * self.out_dim(), es), np.empty(batch * self.in_dim(), es)
+        ga = np.empty(r * self.in_dim(), np.float32) if r else None
+        gb = np.empty(self.out_dim() * r, np.float32) if r else None
+        check(lib.qlc_qlora_forward_backward_host(self._ctx._h, self._h, _p(x), _p(dy), dtype, batch, _p(y), _p(gx), _p(ga),
+                                                  _p(gb)))
+        return y, QloraGrads(ga, gb, gx)
+
+    def forward_backward_host_async(self, x: int, dy: int, batch: int, dtype: int, y: int, grad_x: int,
+                                    grad_a: Optional[int], grad_b: Optional[int]) -> int:
+        """Queues forward + backward on HOST buffers given as addresses (pinned memory for real overlap) and returns
+        a ticket for GpuContext.wait(); the buffers must stay valid and untouched until then."""
+        t = C.c_uint64()
+        check(lib.qlc_qlora_forward_backward_host_async(self._ctx._h, self._h, x, dy, dtype, batch, y, grad_x, grad_a, grad_b,
+                                                        C.byref(t)))
+        return int(t.value)
 
     def forward_dev(self, d_x: int, batch: int, d_y: int, dtype: int = DTYPE_BF16) -> None:
         check(lib.qlc_qlora_forward_dev(self._ctx._h, self._h, d_x, dtype, batch, d_y))

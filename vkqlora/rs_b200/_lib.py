@@ -48,6 +48,8 @@ SIGNATURES = {
     "qlc_ctx_set_precision": (_i, [_vp, _i]),
     "qlc_ctx_synchronize": (_i, [_vp]),
     "qlc_ctx_stream": (_vp, [_vp]),
+    "qlc_ctx_copy_to_host": (_i, [_vp, _vp, _vp, _sz]),
+    "qlc_ctx_copy_to_device": (_i, [_vp, _vp, _vp, _sz]),
     "qlc_ctx_launch_count": (C.c_uint64, [_vp]),
     "qlc_ctx_profile_enable": (_i, [_vp, _i]),
     "qlc_ctx_profile_read": (_i, [_vp, _i, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
@@ -84,6 +86,9 @@ SIGNATURES = {
     "qlc_qlora_backward": (_i, [_vp, _vp, _vp, _sz, _vp, _sz, _sz, _vp, _vp, _vp]),
     "qlc_qlora_forward_host": (_i, [_vp, _vp, _vp, _i, _sz, _vp]),
     "qlc_qlora_backward_host": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _vp]),
+    "qlc_qlora_forward_backward_host": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _vp, _vp]),
+    "qlc_qlora_forward_backward_host_async": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _vp, _vp, C.POINTER(C.c_uint64)]),
+    "qlc_ctx_wait": (_i, [_vp, C.c_uint64]),
     "qlc_qlora_forward_dev": (_i, [_vp, _vp, _vp, _i, _sz, _vp]),
     "qlc_qlora_forward_dev_noalloc": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "qlc_qlora_backward_dev": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _vp]),
@@ -121,6 +126,7 @@ SIGNATURES = {
     "qlc_selftest_nf4_codes_of_targets": (_i, [_vp, C.c_uint32, _sz, _vp, _sz]),
     "qlc_selftest_nf4_fast_path": (_i, [_vp, C.c_float, C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64),
                                         C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
+    "qlc_selftest_adam_math": (_i, [_vp, _i, C.c_uint32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "qlc_selftest_wait_timeout": (_i, [_vp, C.c_uint64]),
 }
 

@@ -287,6 +287,8 @@ int qlc_ctx_destroy(qlc_ctx *ctx) {
     cudaEventDestroy(ctx->ev_fork);
     cudaEventDestroy(ctx->ev_join);
     for (cudaEvent_t e : ctx->chunk_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : ctx->ticket_ev)
+        if (e) cudaEventDestroy(e);
     for (int *p : ctx->d_tile_counters)
         if (p) cudaFree(p);
     delete ctx;
@@ -332,6 +334,24 @@ int qlc_ctx_profile_read(qlc_ctx *ctx, int slot, double *total_ms, uint64_t *lau
     if (launches) *launches = ctx->prof_launches[slot];
     ctx->prof_ms[slot] = 0.0;
     ctx->prof_launches[slot] = 0;
+    return QLC_OK;
+}
+
+int qlc_ctx_copy_to_host(qlc_ctx *ctx, void *dst, const void *d_src, size_t bytes) {
+    if (!ctx) return fail(QLC_ERR_INVALID_CONFIG, "null context");
+    if (bytes == 0) return QLC_OK;
+    if (!dst || !d_src) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
+    QLC_CUDA(cudaSetDevice(ctx->device));
+    QLC_CUDA(cudaMemcpyAsync(dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return QLC_OK;
+}
+
+int qlc_ctx_copy_to_device(qlc_ctx *ctx, void *d_dst, const void *src, size_t bytes) {
+    if (!ctx) return fail(QLC_ERR_INVALID_CONFIG, "null context");
+    if (bytes == 0) return QLC_OK;
+    if (!d_dst || !src) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
+    QLC_CUDA(cudaSetDevice(ctx->device));
+    QLC_CUDA(cudaMemcpyAsync(d_dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     return QLC_OK;
 }
 
@@ -1095,6 +1115,112 @@ int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const voi
     if (L->r && grad_a && na) QLC_CUDA(cudaMemcpyAsync(grad_a, d_ga, na * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (L->r && grad_b && nb) QLC_CUDA(cudaMemcpyAsync(grad_b, d_gb, nb * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return finish_pipelined(ctx);
+}
+
+// Queues forward + backward of one batch (host buffers) without waiting for any of it; *pipelined tells whether the
+// slab pipeline was used (false: the two synchronous calls ran and everything is already complete).
+static int fused_submit(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype, size_t batch, void *y,
+                        void *grad_x, float *grad_a, float *grad_b, bool *pipelined) {
+    *pipelined = false;
+    if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
+    QLC_TRY(same_device(ctx, L));
+    if (dtype != QLC_DTYPE_F32 && dtype != QLC_DTYPE_BF16) return fail(QLC_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
+    const size_t es = dtype_size(dtype), nx = batch * L->in_dim, ny = batch * L->out_dim;
+    const size_t na = L->r * L->in_dim, nb = L->out_dim * L->r;
+    if ((nx && (!x || !grad_x)) || (ny && (!dy || !y))) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
+    QLC_CUDA(cudaSetDevice(ctx->device));
+    bool use_umma = false;
+    QLC_TRY(pick_path(ctx, L, &use_umma));
+    if (!use_umma || dtype != QLC_DTYPE_BF16 || batch < 2 * kSlabRows || ctx->precision == QLC_PRECISION_TF32 || !L->w) {
+        // no pipelined form for this case: the two stateless calls, one after the other
+        QLC_TRY(qlc_qlora_forward_host(ctx, L, x, dtype, batch, y));
+        return qlc_qlora_backward_host(ctx, L, x, dy, dtype, batch, grad_x, grad_a, grad_b);
+    }
+    *pipelined = true;
+    void *io = nullptr;
+    QLC_TRY(ctx_io(ctx, 2 * a256(nx * es) + 2 * a256(ny * es), &io));
+    char *dx = static_cast<char *>(io), *ddy = dx + a256(nx * es), *dyo = ddy + a256(ny * es), *dgx = dyo + a256(ny * es);
+    float *d_ga = L->r ? L->d_grad_bucket : nullptr;
+    float *d_gb = L->r ? L->d_grad_bucket + na : nullptr;
+    // Ordering against what is already queued, without stopping the host:
+    //  * the staged inputs (dx, ddy) are read by the compute of the previous submission: this one's copies in wait
+    //    for the end of that compute (ev_a), not for its copies out - the inbound link keeps working while the
+    //    previous submission's last results are still going out;
+    //  * the staged outputs (dyo, dgx) are read by the previous submission's copies out: the context's stream has
+    //    waited for those (ev_b) at the end of that submission, so this one's compute follows them in stream order.
+    if (!ctx->compute_done_recorded) {
+        QLC_CUDA(cudaEventRecord(ctx->ev_a, ctx->stream));
+        ctx->compute_done_recorded = true;
+    }
+    QLC_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_a, 0));
+    // One pipeline over row slabs: slab c's X and dY go in on the copy stream while slab c-1 computes (forward, then
+    // backward: X crosses the link once and serves both) and the Y and dX of slab c-2 go out on the third stream.
+    const std::vector<size_t> sched = slab_schedule(batch);
+    size_t r0 = 0;
+    for (size_t c = 0; c < sched.size(); r0 += sched[c], ++c) {
+        const size_t rows = sched[c];
+        const size_t ox = r0 * L->in_dim * es, oy = r0 * L->out_dim * es;
+        cudaEvent_t in_done, y_ready, gx_ready;
+        QLC_TRY(chunk_event(ctx, 3 * c, &in_done));
+        QLC_TRY(chunk_event(ctx, 3 * c + 1, &y_ready));
+        QLC_TRY(chunk_event(ctx, 3 * c + 2, &gx_ready));
+        QLC_CUDA(cudaMemcpyAsync(dx + ox, static_cast<const char *>(x) + ox, rows * L->in_dim * es, cudaMemcpyHostToDevice,
+                                 ctx->copy_stream));
+        QLC_CUDA(cudaMemcpyAsync(ddy + oy, static_cast<const char *>(dy) + oy, rows * L->out_dim * es, cudaMemcpyHostToDevice,
+                                 ctx->copy_stream));
+        QLC_CUDA(cudaEventRecord(in_done, ctx->copy_stream));
+        QLC_CUDA(cudaStreamWaitEvent(ctx->stream, in_done, 0));
+        QLC_TRY(umma_qlora_forward(ctx, L, dx + ox, rows, dyo + oy, dtype));
+        QLC_CUDA(cudaEventRecord(y_ready, ctx->stream));
+        QLC_TRY(umma_qlora_backward(ctx, L, reinterpret_cast<const __nv_bfloat16 *>(dx + ox),
+                                    reinterpret_cast<const __nv_bfloat16 *>(ddy + oy), rows, dgx + ox, dtype, d_ga, d_gb,
+                                    c > 0 ? 1 : 0));
+        QLC_CUDA(cudaEventRecord(gx_ready, ctx->stream));
+        QLC_CUDA(cudaStreamWaitEvent(ctx->d2h_stream, y_ready, 0));
+        QLC_CUDA(cudaMemcpyAsync(static_cast<char *>(y) + oy, dyo + oy, rows * L->out_dim * es, cudaMemcpyDeviceToHost,
+                                 ctx->d2h_stream));
+        QLC_CUDA(cudaStreamWaitEvent(ctx->d2h_stream, gx_ready, 0));
+        QLC_CUDA(cudaMemcpyAsync(static_cast<char *>(grad_x) + ox, dgx + ox, rows * L->in_dim * es, cudaMemcpyDeviceToHost,
+                                 ctx->d2h_stream));
+    }
+    if (L->r && grad_a && na) QLC_CUDA(cudaMemcpyAsync(grad_a, d_ga, na * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (L->r && grad_b && nb) QLC_CUDA(cudaMemcpyAsync(grad_b, d_gb, nb * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    QLC_CUDA(cudaEventRecord(ctx->ev_a, ctx->stream));  // end of this submission's compute
+    QLC_CUDA(cudaEventRecord(ctx->ev_b, ctx->d2h_stream));
+    QLC_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_b, 0));  // the context's stream now covers the copies out as well
+    return QLC_OK;
+}
+
+int qlc_qlora_forward_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype, size_t batch,
+                                    void *y, void *grad_x, float *grad_a, float *grad_b) {
+    bool pipelined = false;
+    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, &pipelined));
+    return pipelined ? sync_and_check(ctx) : QLC_OK;
+}
+
+int qlc_qlora_forward_backward_host_async(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype,
+                                          size_t batch, void *y, void *grad_x, float *grad_a, float *grad_b,
+                                          uint64_t *ticket) {
+    if (!ticket) return fail(QLC_ERR_INVALID_CONFIG, "null ticket");
+    bool pipelined = false;
+    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, &pipelined));
+    const uint64_t t = ctx->tickets_issued;
+    cudaEvent_t &ev = ctx->ticket_ev[t % qlc_ctx::kTickets];
+    if (!ev) QLC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    QLC_CUDA(cudaEventRecord(ev, ctx->stream));
+    ctx->tickets_issued = t + 1;
+    *ticket = t;
+    return QLC_OK;
+}
+
+int qlc_ctx_wait(qlc_ctx *ctx, uint64_t ticket) {
+    if (!ctx) return fail(QLC_ERR_INVALID_CONFIG, "null context");
+    if (ticket >= ctx->tickets_issued) return fail(QLC_ERR_INVALID_CONFIG, "ticket %llu was never issued", (unsigned long long)ticket);
+    QLC_CUDA(cudaSetDevice(ctx->device));
+    // An old ticket's event has been re-recorded by a later submission on the same stream: waiting for that one
+    // waits for the older submission too.
+    QLC_CUDA(cudaEventSynchronize(ctx->ticket_ev[ticket % qlc_ctx::kTickets]));
+    return QLC_OK;
 }
 
 // The reference-named fp32 entry points (qlc_qlora_forward / qlc_qlora_backward) promise the reference's

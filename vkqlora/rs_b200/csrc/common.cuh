@@ -63,7 +63,13 @@ struct qlc_ctx {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaStream_t d2h_stream = nullptr;   // device-to-host copies of the pipelined *_host entry points
     std::vector<cudaEvent_t> chunk_events;  // reused by the pipelined *_host entry points
+    // asynchronous host-buffer calls: end of a submission's compute / of its device-to-host copies
     cudaEvent_t ev_a = nullptr, ev_b = nullptr;
+    bool compute_done_recorded = false;
+    // completion tickets of the asynchronous host-buffer calls: a ring of events, ticket t -> ticket_ev[t % 8]
+    static constexpr int kTickets = 8;
+    cudaEvent_t ticket_ev[kTickets] = {nullptr};
+    uint64_t tickets_issued = 0;
     int precision = QLC_PRECISION_AUTO;
     int sm_count = 0;
     uint64_t launches = 0;
