@@ -155,19 +155,23 @@ __device__ __forceinline__ uint32_t nf4_pack8(const float (&v)[8], float am, flo
 // fp32 scales never touch HBM.  Algorithmic traffic: 4 B read + 0.5 B codes + 1/64 B + 4/16384 B
 // written per element.
 constexpr int kQuantThreads = 256;  // measured: 256 beats 128 at every size of the sweep
+// Seven CTAs per SM (36 registers per thread): 148 x 7 = 1036 resident CTAs, so the 1024 super-blocks of a
+// 4096 x 4096 weight run as ONE wave instead of a full wave and a 13 % one, and 8192^2 / 16384^2 as 3.95 / 15.8.
 template <bool kDQ>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, 7)
 quantize_nf4_b64_kernel(const float *__restrict__ w, size_t n, size_t nb, uint8_t *__restrict__ codes,
                         float *__restrict__ scales_f32, uint8_t *__restrict__ absmax_codes,
                         float *__restrict__ absmax2) {
     __shared__ float s_scale[256];
     __shared__ float s_warpmax[kQuantThreads / 32];
     __shared__ float s_thr[16];
+    pdl_trigger();
     const int t = threadIdx.x;
     const size_t sb = blockIdx.x;
     const size_t base = sb * 16384;
     if (t < 15) s_thr[t] = __uint_as_float(c_nf4_thresholds[t]);
     __syncthreads();
+    pdl_wait();  // nothing above touched memory another kernel writes
     float bin_thr;
     uint32_t bin_k;
     nf4_bin_entry(t & 31, s_thr, bin_thr, bin_k);
@@ -329,22 +333,26 @@ dequant_words_kernel(const uint8_t *__restrict__ codes, bool dq, const uint8_t *
 // absmax), then decodes.  Consecutive lanes write consecutive 16-byte pieces, so each store instruction
 // of a warp covers 512 contiguous bytes.  The exact quotients (i8 as f32)/127 come from a 256-entry
 // table computed once per CTA with IEEE division (quant.rs:212-221).
-constexpr int kDeqU = 8;
+// kU = 8 for large tensors; 4 when that leaves fewer than two waves of CTAs (4096 x 4096: the last wave of the
+// larger CTAs was mostly idle).
 
 __device__ __forceinline__ float scale_from(const float *s_q127, bool dq, uint32_t raw, float a2) {
     return dq ? __fmul_rn(s_q127[raw & 255u], a2) : a2;
 }
 
 // fp32 output: thread -> one float4 (4 elements = half a packed word) per unrolled step.
+template <int kDeqU>
 __global__ void __launch_bounds__(256)
 dequant_b64_f32_kernel(const uint32_t *__restrict__ codes, bool dq, const uint8_t *__restrict__ absmax_codes,
                        const float *__restrict__ absmax2, const float *__restrict__ scales_f32, size_t n_quads,
                        float4 *__restrict__ out) {
+    pdl_trigger();
     __shared__ float s_lut[16];
     __shared__ float s_q127[256];
     if (threadIdx.x < 16) s_lut[threadIdx.x] = c_nf4_levels[threadIdx.x];
     s_q127[threadIdx.x] = __fdiv_rn((float)(int8_t)(uint8_t)threadIdx.x, 127.0f);
     __syncthreads();
+    pdl_wait();  // the tables above depend on nothing another kernel writes
     const size_t q0 = (size_t)blockIdx.x * (256 * kDeqU) + threadIdx.x;
     uint32_t w[kDeqU], raw[kDeqU];
     float a2[kDeqU];
@@ -380,15 +388,18 @@ dequant_b64_f32_kernel(const uint32_t *__restrict__ codes, bool dq, const uint8_
 }
 
 // bf16 output: thread -> one packed word (8 elements -> 16 bytes) per unrolled step.
+template <int kDeqU>
 __global__ void __launch_bounds__(256)
 dequant_b64_bf16_kernel(const uint32_t *__restrict__ codes, bool dq, const uint8_t *__restrict__ absmax_codes,
                         const float *__restrict__ absmax2, const float *__restrict__ scales_f32, size_t n_words,
                         uint4 *__restrict__ out) {
+    pdl_trigger();
     __shared__ float s_lut[16];
     __shared__ float s_q127[256];
     if (threadIdx.x < 16) s_lut[threadIdx.x] = c_nf4_levels[threadIdx.x];
     s_q127[threadIdx.x] = __fdiv_rn((float)(int8_t)(uint8_t)threadIdx.x, 127.0f);
     __syncthreads();
+    pdl_wait();  // the tables above depend on nothing another kernel writes
     const size_t g0 = (size_t)blockIdx.x * (256 * kDeqU) + threadIdx.x;
     uint32_t w[kDeqU], raw[kDeqU];
     float a2[kDeqU];
@@ -577,12 +588,14 @@ int launch_quantize_nf4(qlc_ctx *ctx, const float *d_w, qlc_qtensor *q) {
     const bool aligned = (reinterpret_cast<uintptr_t>(d_w) & 15) == 0;
     if (q->block_size == 64 && aligned) {
         const unsigned grid = (unsigned)ceil_div(nb, 256);
+        // launched so that its CTAs may take SMs while the kernel before it in the stream drains (pdl_wait in the
+        // kernel orders its memory accesses behind that kernel's completion)
         if (q->dq)
-            quantize_nf4_b64_kernel<true><<<grid, kQuantThreads, 0, ctx->stream>>>(d_w, n, nb, q->d_codes, nullptr,
-                                                                          q->d_absmax_codes, q->d_absmax2);
+            QLC_CUDA(launch_pdl(quantize_nf4_b64_kernel<true>, dim3(grid), dim3(kQuantThreads), 0, ctx->stream, d_w, n, nb,
+                                q->d_codes, (float *)nullptr, q->d_absmax_codes, q->d_absmax2));
         else
-            quantize_nf4_b64_kernel<false><<<grid, kQuantThreads, 0, ctx->stream>>>(d_w, n, nb, q->d_codes, q->d_scales_f32,
-                                                                           nullptr, nullptr);
+            QLC_CUDA(launch_pdl(quantize_nf4_b64_kernel<false>, dim3(grid), dim3(kQuantThreads), 0, ctx->stream, d_w, n, nb,
+                                q->d_codes, q->d_scales_f32, (uint8_t *)nullptr, (float *)nullptr));
         ctx->launches += 1;
     } else {
         float *scales = q->d_scales_f32;
@@ -613,19 +626,31 @@ static int launch_dequantize_t(qlc_ctx *ctx, const qlc_qtensor *q, OutT *d_out) 
     size_t word0 = 0;  // first packed word the generic kernel still has to do
     if (q->block_size == 64 && out_aligned) {
         // whole CTAs of the streaming kernel, the remainder goes to the generic word kernel
-        constexpr size_t kElemsPerCta = std::is_same<OutT, float>::value ? 256 * kDeqU * 4 : 256 * kDeqU * 8;
-        const size_t ctas = n / kElemsPerCta;
+        constexpr bool kF32 = std::is_same<OutT, float>::value;
+        constexpr size_t kElemsPerStep = kF32 ? 256 * 4 : 256 * 8;  // one unrolled step of a CTA
+        // CTAs of 8 steps, or of 4 when 8 would leave fewer than ~3 waves of resident CTAs (about 6 per SM)
+        const size_t small_limit = (size_t)ctx->sm_count * 6 * 3;
+        const int u = (n / (8 * kElemsPerStep) < small_limit) ? 4 : 8;
+        const size_t ctas = n / (u * kElemsPerStep);
         if (ctas > 0) {
-            if (std::is_same<OutT, float>::value)
-                dequant_b64_f32_kernel<<<(unsigned)ctas, 256, 0, ctx->stream>>>(
-                    reinterpret_cast<const uint32_t *>(q->d_codes), q->dq, q->d_absmax_codes, q->d_absmax2,
-                    q->d_scales_f32, ctas * (kElemsPerCta / 4), reinterpret_cast<float4 *>(d_out));
+            const uint32_t *codes = reinterpret_cast<const uint32_t *>(q->d_codes);
+            const size_t units = ctas * u * 256;
+            const bool dq = q->dq;
+            float4 *of = reinterpret_cast<float4 *>(d_out);
+            uint4 *ob = reinterpret_cast<uint4 *>(d_out);
+            const dim3 g((unsigned)ctas), b(256);
+            cudaError_t e;
+            if (kF32 && u == 8)
+                e = launch_pdl(dequant_b64_f32_kernel<8>, g, b, 0, ctx->stream, codes, dq, q->d_absmax_codes, q->d_absmax2, q->d_scales_f32, units, of);
+            else if (kF32)
+                e = launch_pdl(dequant_b64_f32_kernel<4>, g, b, 0, ctx->stream, codes, dq, q->d_absmax_codes, q->d_absmax2, q->d_scales_f32, units, of);
+            else if (u == 8)
+                e = launch_pdl(dequant_b64_bf16_kernel<8>, g, b, 0, ctx->stream, codes, dq, q->d_absmax_codes, q->d_absmax2, q->d_scales_f32, units, ob);
             else
-                dequant_b64_bf16_kernel<<<(unsigned)ctas, 256, 0, ctx->stream>>>(
-                    reinterpret_cast<const uint32_t *>(q->d_codes), q->dq, q->d_absmax_codes, q->d_absmax2,
-                    q->d_scales_f32, ctas * (kElemsPerCta / 8), reinterpret_cast<uint4 *>(d_out));
+                e = launch_pdl(dequant_b64_bf16_kernel<4>, g, b, 0, ctx->stream, codes, dq, q->d_absmax_codes, q->d_absmax2, q->d_scales_f32, units, ob);
+            QLC_CUDA(e);
             ctx->launches += 1;
-            word0 = ctas * kElemsPerCta / 8;
+            word0 = ctas * u * kElemsPerStep / 8;
         }
     }
     if (word0 * 8 < n) {
