@@ -1232,6 +1232,8 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 
+#include "umma_gemm3.cuh"
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1436,6 +1438,22 @@ int launch_gemm2(qlc_ctx *ctx, int prof_slot, const CUtensorMap &tA, const CUten
         return launch_with_timing(ctx, grid, args, [&](const GemmArgs &a) {
             kern<<<grid, kThreads2, smem, ctx->stream>>>(tA, tAe, tBe, tOut, a);
         });
+    // Default: the persistent kernel, one wave of CTA pairs that walk the same item list (QLC_GEMM_ONE_TILE_PER_PAIR
+    // selects the one-item-per-pair kernel above, for A/B measurements).
+    static const bool one_tile = getenv("QLC_GEMM_ONE_TILE_PER_PAIR") != nullptr;
+    if (!one_tile) {
+        auto kern3 = umma_gemm3_kernel<B_MN, TF32>;
+        if ((size_t)ctx->umma_smem_optin < kSmem3)
+            return fail(QLC_ERR_GPU, "kernel needs %zu bytes of shared memory, device allows %d", kSmem3, ctx->umma_smem_optin);
+        QLC_CUDA(cudaFuncSetAttribute(kern3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem3));
+        const uint32_t pairs = items < (uint32_t)ctx->sm_count / 2 ? items : (uint32_t)ctx->sm_count / 2;
+        prof_begin(ctx, prof_slot);
+        QLC_CUDA(launch_pdl(kern3, dim3(2 * pairs), dim3(kThreads3), kSmem3, ctx->stream, tA, tAe, tBe, tOut, args));
+        prof_end(ctx);
+        ctx->launches += 1;
+        QLC_CUDA(cudaGetLastError());
+        return QLC_OK;
+    }
     prof_begin(ctx, prof_slot);
     QLC_CUDA(launch_pdl(kern, grid, dim3(kThreads2), smem, ctx->stream, tA, tAe, tBe, tOut, args));
     prof_end(ctx);
