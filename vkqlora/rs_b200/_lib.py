@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libqlora_cuda.so")
+# QLORA_CUDA_LIBRARY names another build of the library (A/B measurements of two builds in one process tree)
+LIB_PATH = os.environ.get("QLORA_CUDA_LIBRARY") or os.path.join(_HERE, "libqlora_cuda.so")
 
 OK, ERR_SHAPE_MISMATCH, ERR_INVALID_CONFIG, ERR_GPU = 0, 1, 2, 3
 DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2

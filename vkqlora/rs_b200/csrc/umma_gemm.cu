@@ -1434,10 +1434,41 @@ int launch_gemm2(qlc_ctx *ctx, int prof_slot, const CUtensorMap &tA, const CUten
     }
     dim3 grid(2 * items, 1, 1);
     static const bool dump_timing = getenv("QLC_GEMM_TIMING") != nullptr;
-    if (dump_timing)
+    static const bool one_tile_t = getenv("QLC_GEMM_ONE_TILE_PER_PAIR") != nullptr;
+    if (dump_timing && one_tile_t)
         return launch_with_timing(ctx, grid, args, [&](const GemmArgs &a) {
             kern<<<grid, kThreads2, smem, ctx->stream>>>(tA, tAe, tBe, tOut, a);
         });
+    if (dump_timing) {
+        // the persistent kernel's own sums: per leader CTA, cycles
+        auto kern3 = umma_gemm3_kernel<B_MN, TF32, true>;
+        QLC_CUDA(cudaFuncSetAttribute(kern3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem3));
+        const uint32_t pairs = items < (uint32_t)ctx->sm_count / 2 ? items : (uint32_t)ctx->sm_count / 2;
+        const size_t ctas = 2 * (size_t)pairs;
+        long long *d = nullptr;
+        QLC_CUDA(cudaMalloc(&d, ctas * 16 * sizeof(long long)));
+        QLC_CUDA(cudaMemsetAsync(d, 0, ctas * 16 * sizeof(long long), ctx->stream));
+        args.timing = d;
+        kern3<<<dim3(2 * pairs), kThreads3, kSmem3, ctx->stream>>>(tA, tAe, tBe, tOut, args);
+        ctx->launches += 1;
+        QLC_CUDA(cudaStreamSynchronize(ctx->stream));
+        std::vector<long long> h(ctas * 16);
+        QLC_CUDA(cudaMemcpy(h.data(), d, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+        cudaFree(d);
+        double tot = 0, issue = 0, wfull = 0, wfirst = 0, wa0 = 0, wa1 = 0, eidle = 0, e0 = 0, e1 = 0, pw = 0, nd = 0;
+        for (size_t i = 0; i < ctas; i += 2) {  // leaders
+            const long long *t = &h[16 * i];
+            tot += t[11] - t[0]; issue += t[1] - t[0]; wfull += t[2]; wfirst += t[3]; wa0 += t[4]; wa1 += t[5];
+            eidle += t[6]; e0 += t[7]; e1 += t[8]; nd += t[9]; pw += t[10];
+        }
+        const double n = (double)pairs;
+        fprintf(stderr, "[qlc timing3] %u pairs, %u items (%.2f per pair), %u+%u steps: life %.0f | mma issue span %.0f | mma waits: full %.0f, "
+                        "first full of an item %.0f, acc0 %.0f, acc1 %.0f | epilogue: idle %.0f, to acc0 release %.0f, to acc1 release %.0f | "
+                        "producer group 0 waiting %.0f  [cycles per pair, sums over its items]\n",
+                pairs, items, nd / n, args.k_steps, args.ext_steps, tot / n, issue / n, wfull / n, wfirst / n, wa0 / n, wa1 / n, eidle / n,
+                e0 / n, e1 / n, pw / n);
+        return QLC_OK;
+    }
     // Default: the persistent kernel, one wave of CTA pairs that walk the same item list (QLC_GEMM_ONE_TILE_PER_PAIR
     // selects the one-item-per-pair kernel above, for A/B measurements).
     static const bool one_tile = getenv("QLC_GEMM_ONE_TILE_PER_PAIR") != nullptr;

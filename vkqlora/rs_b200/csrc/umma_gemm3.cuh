@@ -53,7 +53,8 @@ __device__ __forceinline__ Item3 decode_item3(const GemmArgs &args, uint32_t ite
     return w;
 }
 
-template <bool B_MN, bool TF32 = false>
+// TIMING: the diagnostics build (clock64 sums per role).
+template <bool B_MN, bool TF32 = false, bool TIMING = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads3, 1)
 umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAext,
                   const __grid_constant__ CUtensorMap tmBext, const __grid_constant__ CUtensorMap tmOut,
@@ -95,6 +96,9 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    // diagnostics (QLC_GEMM_TIMING): 16 clock64 sums / stamps per CTA
+    long long *const tstamp = (TIMING && args.timing) ? args.timing + 16 * (size_t)blockIdx.x : nullptr;
+    if (tstamp && threadIdx.x == 0) tstamp[0] = clock64();
     const uint32_t items = args.full_items + (args.k_chunks > 1 ? (args.row_tiles * args.col_tiles - args.full_items) * args.k_chunks : 0u);
 
     if (threadIdx.x == 0) {
@@ -130,7 +134,8 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();  // everything above touched no memory an earlier kernel writes (the status word is only ever raised)
 
-    if (warp == 0) {
+    if (warp < kCtlWarps3) {
+      if (warp == 0) {
         // ---------------- TMA issue (both CTAs; completion is reported to the leader's barrier) -----------
         if (lane == 0) {
             uint32_t g = 0;  // stage uses so far
@@ -167,7 +172,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ---------------- MMA issue (leader CTA only) ----------------
         if (leader && lane == 0) {
             constexpr uint32_t kFmt = TF32 ? 2u : 1u;  // operand format: bf16 = 1, tf32 = 2; accumulator fp32 = 1
@@ -175,51 +180,96 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
             uint32_t g = 0, n_done = 0;
             bool ok = true;
+            long long t_full = 0, t_first = 0, t_acc[2] = {0, 0};
+            // One thread issues every MMA of the pair: whatever it executes between two MMAs is time the tensor
+            // cores may sit idle.  The 64-bit operand descriptors are therefore not rebuilt per instruction: their
+            // high words (stride, version, swizzle mode) are constants, and the low word is the stage's base value
+            // plus a small multiple of the k-slice (the start-address field counts 16-byte units and never carries
+            // into the next field).  Barrier addresses in the peer CTA are looked up once.
+            const uint64_t da0 = make_desc(smem_base, 16, 1024);
+            const uint64_t db0 = B_MN ? make_desc(smem_base + kABytes2, kAtomBytes, TF32 ? 512u : 1024u, TF32 ? 1u : 2u)
+                                      : make_desc(smem_base + kABytes2, 16, 1024);
+            const uint32_t da_hi = (uint32_t)(da0 >> 32), da_lo0 = (uint32_t)da0;
+            const uint32_t db_hi = (uint32_t)(db0 >> 32), db_lo0 = (uint32_t)db0;
+            constexpr uint32_t kStage16 = kStageBytes2 >> 4, kAcc16 = (kBM * 128) >> 4;
+            constexpr uint32_t kBk16 = B_MN ? (kMnStep >> 4) : 2u;  // B operand: 16-byte units per k-slice
+            uint32_t empty_remote[kStages2][2];
+#pragma unroll
+            for (int st = 0; st < kStages2; ++st) {
+                empty_remote[st][0] = mapa_u32(empty_bar(st), 0);
+                empty_remote[st][1] = mapa_u32(empty_bar(st), 1);
+            }
+            const uint32_t tfull_remote[2] = {mapa_u32(tmem_full_bar, 0), mapa_u32(tmem_full_bar, 1)};
+            auto desc64 = [](uint32_t lo, uint32_t hi) {
+                uint64_t d;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+                return d;
+            };
             for (uint32_t item = pair_id; item < items && ok; item += n_pairs, ++n_done) {
                 const Item3 w = decode_item3(args, item, rank);
-                for (uint32_t it = 0; it < w.total_steps; ++it, ++g) {
-                    const int s = g % kStages2;
-                    const uint32_t ph = (g / kStages2) & 1u;
-                    if (!mbar_wait(full_bar(s), ph, abort_flag, args.status, 32)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t a_src = smem_base + s * kStageBytes2;
-                    const uint32_t b_src = a_src + kABytes2;
+                uint32_t it = 0;
+                while (it < w.total_steps && ok) {
+                    // the stage index is a compile-time constant inside this block: the four cases are the same
+                    // code with different immediates
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        // the first MMA of an item overwrites accumulator a: both CTAs' epilogue warps must have
-                        // read the previous item's values out of it
-                        if (it == 0) {
-                            if (!mbar_wait(acc_empty_bar(a), (n_done & 1u) ^ 1u, abort_flag, args.status, 37)) {
-                                ok = false;
-                                break;
+                    for (int st = 0; st < kStages2; ++st) {
+                        if ((g & (kStages2 - 1)) != (uint32_t)st || it >= w.total_steps || !ok) continue;
+                        const uint32_t ph = (g / kStages2) & 1u;
+                        const long long tw = tstamp ? clock64() : 0;
+                        if (!mbar_wait(full_bar(st), ph, abort_flag, args.status, 32)) {
+                            ok = false;
+                            break;
+                        }
+                        if (tstamp) (it == 0 ? t_first : t_full) += clock64() - tw;  // waiting for a full stage
+                        tc_fence_after();
+                        const uint32_t a_lo = da_lo0 + st * kStage16, b_lo = db_lo0 + st * kStage16;
+#pragma unroll
+                        for (int a = 0; a < 2; ++a) {
+                            // the first MMA of an item overwrites accumulator a: both CTAs' epilogue warps must have
+                            // read the previous item's values out of it
+                            if (it == 0) {
+                                const long long ta = tstamp ? clock64() : 0;
+                                if (!mbar_wait(acc_empty_bar(a), (n_done & 1u) ^ 1u, abort_flag, args.status, 37)) {
+                                    ok = false;
+                                    break;
+                                }
+                                if (tstamp) t_acc[a] += clock64() - ta;  // waiting for the epilogue to hand accumulator a back
+                                tc_fence_after();
                             }
-                            tc_fence_after();
-                        }
 #pragma unroll
-                        for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-                            const uint64_t da = make_desc(a_src + a * (kBM * 128) + kk * 32, 16, 1024);
-                            const uint64_t db = B_MN ? make_desc(b_src + kk * kMnStep, kAtomBytes, TF32 ? 512u : 1024u, TF32 ? 1u : 2u)
-                                                     : make_desc(b_src + kk * 32, 16, 1024);
-                            if (TF32)
-                                umma2_tf32(tmem_base + a * BN, da, db, idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                            else
-                                umma2_bf16(tmem_base + a * BN, da, db, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+                                const uint64_t da = desc64(a_lo + a * kAcc16 + kk * 2, da_hi);
+                                const uint64_t db = desc64(b_lo + kk * kBk16, db_hi);
+                                const uint32_t acc = (kk > 0) ? 1u : (it > 0 ? 1u : 0u);
+                                if (TF32)
+                                    umma2_tf32(tmem_base + a * BN, da, db, idesc, acc);
+                                else
+                                    umma2_bf16(tmem_base + a * BN, da, db, idesc, acc);
+                            }
                         }
+                        if (!ok) break;
+                        umma2_commit(empty_remote[st][0]);
+                        umma2_commit(empty_remote[st][1]);
+                        ++it;
+                        ++g;
                     }
-                    if (!ok) break;
-                    umma2_commit(mapa_u32(empty_bar(s), 0));
-                    umma2_commit(mapa_u32(empty_bar(s), 1));
                 }
                 if (ok) {
-                    umma2_commit(mapa_u32(tmem_full_bar, 0));
-                    umma2_commit(mapa_u32(tmem_full_bar, 1));
+                    umma2_commit(tfull_remote[0]);
+                    umma2_commit(tfull_remote[1]);
                 }
+            }
+            if (tstamp) {
+                tstamp[1] = clock64();  // all MMAs issued
+                tstamp[2] = t_full;
+                tstamp[3] = t_first;
+                tstamp[4] = t_acc[0];
+                tstamp[5] = t_acc[1];
+                tstamp[9] = n_done;
             }
         }
         __syncwarp();
+      }
     } else if (warp < kCtlWarps3 + kProdWarps3) {
         // ---------------- weight-tile producers (two groups, alternate stage uses) ----------
         const int group = (warp - kCtlWarps3) / kGroupWarps2;
@@ -227,6 +277,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int hf = pt & 1;
         uint32_t g0 = 0;  // stage uses before the current item
         bool ok = true;
+        long long t_pw = 0;
         for (uint32_t item = pair_id; item < items && ok; item += n_pairs) {
             const Item3 w = decode_item3(args, item, rank);
             const uint32_t first = ((g0 & 1u) == (uint32_t)group) ? 0u : 1u;  // this group's first step of the item
@@ -372,10 +423,12 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     // (code as i8 as f32) / 127 * absmax2[blk / 256]   (quant.rs:212-221); exact quotients from the table
                     const float scale = args.dq ? __fmul_rn(s_q127[nraw & 255u], na2) : na2;
                     if (valid && it + 2 < w.main_steps) fetch(it + 2, nc, nraw, na2);
+                    const long long tp = tstamp ? clock64() : 0;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, 33)) {
                         ok = false;
                         break;
                     }
+                    if (tstamp) t_pw += clock64() - tp;  // waiting for an empty stage
                     if (!ext) {
                         const uint32_t dst = smem_base + s * kStageBytes2 + kABytes2;
                         if (valid) {
@@ -403,6 +456,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             g0 += w.total_steps;
         }
+        if (tstamp && pt == 0 && group == 0) tstamp[10] = t_pw;
     } else {
         // ---------------- epilogue warps: accumulators -> registers -> (bf16: shared-memory slab -> TMA store) --------
         const int ew = warp - (kCtlWarps3 + kProdWarps3);  // 0..3
@@ -412,6 +466,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t slabs = epi_base + (uint32_t)ew * 2u * kEpiSlabBytes3;
         const size_t piece_floats = (size_t)2 * kBM * BN;
         uint32_t n_done = 0, cut_seen = 0, slab_flip = 0;
+        long long t_idle = 0, t_rel[2] = {0, 0};
         // hands accumulator a back to the MMA thread (every lane's tcgen05.ld of it has completed)
         auto release_acc = [&](int a) {
             tc_fence_before();
@@ -421,7 +476,10 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         bool ok = true;
         for (uint32_t item = pair_id; item < items && ok; item += n_pairs, ++n_done) {
             const Item3 w = decode_item3(args, item, rank);
+            const long long te0 = tstamp ? clock64() : 0;
             if (!mbar_wait(tmem_full_bar, n_done & 1u, abort_flag, args.status, 34)) break;
+            const long long te1 = tstamp ? clock64() : 0;
+            t_idle += te1 - te0;  // epilogue idle, waiting for accumulators
             tc_fence_after();
             // A piece of a cut tile first leaves its accumulators as an fp32 partial.  The CTA whose partial
             // completes the tile then builds the result from all partials, always adding them in chunk order, so
@@ -530,6 +588,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         }
                     }
                     if (!w.cut) release_acc(a);
+                    if (tstamp) t_rel[a] += clock64() - te1;  // accumulators complete -> accumulator a handed back
                 }
             } else {
 #pragma unroll 1
@@ -553,6 +612,11 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 }
             }
         }
+        if (tstamp && et == 0) {
+            tstamp[6] = t_idle;
+            tstamp[7] = t_rel[0];
+            tstamp[8] = t_rel[1];
+        }
         // the slabs must stay in place until the TMA engine has read the last stores
         if (lane == 0) tma_store_commit_and_wait_read();
         __syncwarp();
@@ -564,6 +628,7 @@ umma_gemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncthreads();
     pause_after_abort(abort_flag);
     cluster_sync_all();
+    if (tstamp && threadIdx.x == 0) tstamp[11] = clock64();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
