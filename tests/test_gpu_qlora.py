@@ -150,6 +150,10 @@ def _assert_close(name, got, want, rows, cols, tol=TOL_BF16):
     (512, 320, 8, 300),     # ragged rows, several k-steps, two column tiles
     (576, 576, 8, 32),      # BASELINE config 1 shape: partial column tile, few rows
     (320, 1024, 64, 1000),  # rank 64
+    (256, 256, 5, 70),      # the reference GPU test's rank (qlora-wgpu/tests/gpu_backward.rs:60)
+    (320, 256, 96, 300),    # ranks above 64: the rank-padded products run in 64-column slices
+    (256, 384, 130, 200),   # three slices, the last one nearly empty
+    (256, 256, 256, 128),   # the largest rank the tensor-core path takes
 ])
 def test_tensor_core_path_vs_oracle(v, oracle, tc_ctx, out_dim, in_dim, r, batch):
     layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch)
@@ -386,6 +390,7 @@ def tf32_ctx(v):
     (512, 320, 8, 300),     # ragged rows, several k-steps, two column tiles
     (576, 576, 8, 32),      # BASELINE config 1 shape
     (320, 1024, 64, 1000),  # rank 64, cut tiles
+    (320, 256, 96, 300),    # rank above 64 (two 64-column slices)
 ])
 def test_tf32_mode_vs_oracle(v, oracle, tf32_ctx, out_dim, in_dim, r, batch):
     _tf32_case(v, oracle, tf32_ctx, out_dim, in_dim, r, batch, None)

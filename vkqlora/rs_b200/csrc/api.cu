@@ -840,7 +840,7 @@ static int pick_path(qlc_ctx *ctx, const qlc_layer *L, bool *use_umma) {
     } else if (ctx->precision == QLC_PRECISION_BF16 || ctx->precision == QLC_PRECISION_TF32) {
         if (!ok)
             return fail(QLC_ERR_GPU,
-                        "tensor-core path needs block_size 32, 64, 128 or 256, in_dim/out_dim multiples of 64 and rank <= 64 "
+                        "tensor-core path needs block_size 32, 64, 128 or 256, in_dim/out_dim multiples of 64 and rank <= 256 "
                         "(got block %zu, in %zu, out %zu, r %zu)",
                         L->w ? L->w->block_size : (size_t)0, L->in_dim, L->out_dim, L->r);
         *use_umma = true;

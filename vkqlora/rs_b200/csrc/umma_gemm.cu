@@ -52,6 +52,7 @@ constexpr int kUmmaK = 16;       // contraction per tcgen05.mma (bf16)
 template <bool B_DEQUANT> constexpr int kWorkerWarps = B_DEQUANT ? 16 : 8;
 template <bool B_DEQUANT> constexpr int kBlockThreads = 32 * (2 + kWorkerWarps<B_DEQUANT>);
 constexpr int kRankPad = 64;     // LoRA rank is zero-padded to a multiple of this
+constexpr int kMaxRank = 256;    // ranks the tensor-core path takes (rank-padded products in slices of 64 columns)
 
 __constant__ float c_levels[16] = {
     (float)-1.0,
@@ -107,6 +108,7 @@ struct GemmArgs {
     float *final1, *final2;
     int transposed1, transposed2;  // final is (cols_used, M) row-major instead of (M, cols_used)
     uint32_t cols_used;
+    uint32_t final_ld;  // row pitch of a non-transposed final (0: cols_used), for a column slice of a wider matrix
     int accumulate;     // final += sum instead of final = sum
     // Paired-CTA weight GEMM: work items in launch order.  Items [0, full_items) are whole output tiles;
     // the tiles of the last, partial wave follow, each cut into k_chunks pieces along the contraction so
@@ -596,7 +598,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const uint32_t lr = transposed ? i % rows_here : i / cu;
                     const uint32_t c = transposed ? i / rows_here : i % cu;
                     const uint32_t r = m0 + lr;
-                    const size_t oi = transposed ? (size_t)c * Mrows + r : (size_t)r * cu + c;
+                    const size_t oi = transposed ? (size_t)c * Mrows + r : (size_t)r * (args.final_ld ? args.final_ld : cu) + c;
                     float v[16];  // at most 16 splits; all loads are issued before the first add
 #pragma unroll
                     for (uint32_t zz = 0; zz < 16; ++zz)
@@ -1256,16 +1258,18 @@ int get_encode_fn(EncodeTiledFn *out) {
 // bf16 row-major (rows, cols) matrix; box = 64 columns (128 bytes, swizzled) x box_rows rows.
 // Row-major (rows, cols) matrix of bf16 (or fp32 when `f32`), boxes of one 128-byte row segment x box_rows rows.
 // swizzle32: 32-byte swizzle chunks, for tiles that the tensor core reads as MN-major 32-bit operands.
+// pitch: elements between rows (0: the rows are contiguous, pitch = cols), for column slices of a wider matrix.
 int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool f32 = false,
-             bool swizzle32 = false) {
+             bool swizzle32 = false, uint64_t pitch = 0) {
     EncodeTiledFn enc = nullptr;
     QLC_TRY(get_encode_fn(&enc));
     const uint64_t es = f32 ? 4 : 2;
-    if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols * es) % 16)
+    if (!pitch) pitch = cols;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch * es) % 16)
         return fail(QLC_ERR_GPU, "tensor map: base %p / row pitch %llu bytes must be 16-byte aligned", base,
-                    (unsigned long long)(cols * es));
+                    (unsigned long long)(pitch * es));
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * es};
+    const cuuint64_t strides[1] = {pitch * es};
     const cuuint32_t box[2] = {f32 ? 32u : 64u, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
@@ -1577,7 +1581,7 @@ bool umma_supported(const qlc_layer *L) {
     const qlc_qtensor *q = L->w;
     const bool block_ok = q->block_size == 32 || q->block_size == 64 || q->block_size == 128 || q->block_size == 256;
     return block_ok && L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
-           L->r <= (size_t)kRankPad && L->in_dim < (1u << 30) && L->out_dim < (1u << 30);
+           L->r <= (size_t)kMaxRank && L->in_dim < (1u << 30) && L->out_dim < (1u << 30);
 }
 
 void umma_layer_release(qlc_layer *) {}
@@ -1593,16 +1597,34 @@ struct DownJob {
     const void *src;   // (batch, cols) activations: bf16, or fp32 in TF32 mode
     size_t cols;
     const void *low;   // (r_pad, cols) padded adapter matrix of the same type
-    void *out;         // (batch, 64) of the same type
+    void *out;         // (batch, r_pad) of the same type
 };
 template <bool TF32>
+static int lora_down_slice(qlc_ctx *ctx, qlc_layer *L, size_t batch, const DownJob *jobs, int n_jobs);
+// Ranks above 64: the padded rank is covered in slices of 64 columns, one launch (or paired launch) per slice;
+// slice s reads rows 64s.. of the padded adapter matrix and writes columns 64s.. of the (batch, r_pad) result.
+template <bool TF32>
 static int lora_down_t(qlc_ctx *ctx, qlc_layer *L, size_t batch, const DownJob *jobs, int n_jobs) {
+    const size_t es = TF32 ? 4 : 2;
+    for (size_t sl = 0; sl < L->r_pad / kRankPad; ++sl) {
+        DownJob j2[2];
+        for (int j = 0; j < n_jobs; ++j) {
+            j2[j] = jobs[j];
+            j2[j].low = static_cast<const char *>(jobs[j].low) + sl * kRankPad * jobs[j].cols * es;
+            j2[j].out = static_cast<char *>(jobs[j].out) + sl * kRankPad * es;
+        }
+        QLC_TRY(lora_down_slice<TF32>(ctx, L, batch, j2, n_jobs));
+    }
+    return QLC_OK;
+}
+template <bool TF32>
+static int lora_down_slice(qlc_ctx *ctx, qlc_layer *L, size_t batch, const DownJob *jobs, int n_jobs) {
     const uint32_t nn = L->r <= 16 ? 16u : (L->r <= 32 ? 32u : 64u);
     constexpr uint32_t kStep = TF32 ? 32 : 64;
     CUtensorMap tS[2], tL[2];
     for (int j = 0; j < n_jobs; ++j) {
         QLC_TRY(make_map(&tS[j], jobs[j].src, batch, jobs[j].cols, 64, TF32));
-        QLC_TRY(make_map(&tL[j], jobs[j].low, L->r_pad, jobs[j].cols, nn, TF32));
+        QLC_TRY(make_map(&tL[j], jobs[j].low, kRankPad, jobs[j].cols, nn, TF32));
     }
     if (n_jobs == 1) {
         tS[1] = tS[0];
@@ -1614,7 +1636,7 @@ static int lora_down_t(qlc_ctx *ctx, qlc_layer *L, size_t batch, const DownJob *
     a.N = nn;
     a.k_steps = (uint32_t)(jobs[0].cols / kStep);
     a.out = jobs[0].out;
-    a.ldo = kRankPad;
+    a.ldo = (uint32_t)L->r_pad;
     a.out_bf16 = TF32 ? 0 : 1;
     a.out_pad_cols = kRankPad;
     a.out_scale = L->alpha / (float)L->r;  // lora.rs:64-66
@@ -1645,20 +1667,40 @@ static int lora_down_x(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *d_x, siz
 struct ContractJob {
     const void *p;   // (batch, wide) activations: bf16, or fp32 in TF32 mode
     size_t wide;
-    const void *q;   // (batch, 64) of the same type
+    const void *q;   // (batch, r_pad) of the same type
     int transposed;
     float *out;
 };
 template <bool TF32>
+static int token_contract_slice(qlc_ctx *ctx, qlc_layer *L, size_t batch, const ContractJob *jobs, int n_jobs,
+                                float *partial, int accumulate, cudaStream_t stream, size_t sl);
+// Ranks above 64: one launch per 64-column slice of Q; slice s produces rows 64s.. of a transposed result
+// (dA: (r, wide)) or columns 64s.. of a plain one (dB: (wide, r)).
+template <bool TF32>
 static int token_contract_t(qlc_ctx *ctx, qlc_layer *L, size_t batch, const ContractJob *jobs, int n_jobs,
                             float *partial, int accumulate, cudaStream_t stream) {
+    const size_t es = TF32 ? 4 : 2;
+    for (size_t sl = 0; sl * kRankPad < L->r; ++sl) {
+        ContractJob j2[2];
+        for (int j = 0; j < n_jobs; ++j) {
+            j2[j] = jobs[j];
+            j2[j].q = static_cast<const char *>(jobs[j].q) + sl * kRankPad * es;
+            j2[j].out = jobs[j].out + (jobs[j].transposed ? sl * kRankPad * jobs[j].wide : sl * kRankPad);
+        }
+        QLC_TRY(token_contract_slice<TF32>(ctx, L, batch, j2, n_jobs, partial, accumulate, stream, sl));
+    }
+    return QLC_OK;
+}
+template <bool TF32>
+static int token_contract_slice(qlc_ctx *ctx, qlc_layer *L, size_t batch, const ContractJob *jobs, int n_jobs,
+                                float *partial, int accumulate, cudaStream_t stream, size_t sl) {
     constexpr uint32_t kStep = TF32 ? 32 : 64;
     const size_t batch_pad = (batch + kStep - 1) / kStep * kStep;  // rows past `batch` read as zeros through TMA
     CUtensorMap tP[2], tQ[2];
     uint32_t tiles = 0, tiles_max = 0;
     for (int j = 0; j < n_jobs; ++j) {
         QLC_TRY(make_map(&tP[j], jobs[j].p, batch, jobs[j].wide, kStep, TF32, TF32));
-        QLC_TRY(make_map(&tQ[j], jobs[j].q, batch, kRankPad, kStep, TF32, TF32));
+        QLC_TRY(make_map(&tQ[j], jobs[j].q, batch, kRankPad, kStep, TF32, TF32, L->r_pad));
         const uint32_t t = (uint32_t)ceil_div(jobs[j].wide, 128);
         tiles += t;
         if (t > tiles_max) tiles_max = t;
@@ -1677,7 +1719,8 @@ static int token_contract_t(qlc_ctx *ctx, qlc_layer *L, size_t batch, const Cont
     a.out_bf16 = 0;
     a.final1 = jobs[0].out;
     a.transposed1 = jobs[0].transposed;
-    a.cols_used = (uint32_t)L->r;
+    a.cols_used = (uint32_t)(L->r - sl * kRankPad < (size_t)kRankPad ? L->r - sl * kRankPad : (size_t)kRankPad);
+    a.final_ld = (uint32_t)L->r;
     a.accumulate = accumulate;
     if (n_jobs == 2) {
         a.pair = 1;
@@ -1709,16 +1752,17 @@ int umma_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, size_t batch
     const size_t es = tf32 ? 4 : 2, step = tf32 ? 32 : 64;
     void *ws = nullptr;
     const size_t cut_bytes = use_paired_ctas() ? kcut_bytes(ctx, batch, L->out_dim, L->in_dim / step) : 0;
-    QLC_TRY(ctx_workspace(ctx, a256(batch * kRankPad * es) + cut_bytes, &ws));
+    const size_t rp = L->r_pad ? L->r_pad : (size_t)kRankPad;  // columns of the rank-padded intermediates
+    QLC_TRY(ctx_workspace(ctx, a256(batch * rp * es) + cut_bytes, &ws));
     void *t1p = ws;
-    float *split_ws = cut_bytes ? reinterpret_cast<float *>(static_cast<char *>(ws) + a256(batch * kRankPad * es)) : nullptr;
+    float *split_ws = cut_bytes ? reinterpret_cast<float *>(static_cast<char *>(ws) + a256(batch * rp * es)) : nullptr;
     CUtensorMap tX, tT1, tB;
     QLC_TRY(make_map(&tX, d_x, batch, L->in_dim, 128, tf32));
     GemmArgs a = base_args(ctx, L);
     if (L->r > 0) {
         const DownJob job{d_x, L->in_dim, tf32 ? (const void *)L->d_a_pad32 : (const void *)L->d_a_pad, t1p};  // T1p = s·X·A^T
         QLC_TRY(lora_down(ctx, L, batch, &job, 1, tf32));
-        QLC_TRY(make_map(&tT1, t1p, batch, kRankPad, 128, tf32));
+        QLC_TRY(make_map(&tT1, t1p, batch, rp, 128, tf32));
         QLC_TRY(make_map(&tB, tf32 ? (const void *)L->d_b_pad32 : (const void *)L->d_b_pad, L->out_dim, L->r_pad,
                          use_paired_ctas() ? 128 : 256, tf32));
         a.ext_steps = (uint32_t)(L->r_pad / step);
@@ -1758,6 +1802,9 @@ int umma_qlora_forward_noalloc(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *
                     "qlc_qlora_forward_dev_noalloc handles at most %zu rows per call (its scratch is a fixed "
                     "%zu-byte device array); got %zu rows - split the batch or use qlc_qlora_forward_dev",
                     kNoAllocMaxRows, sizeof(g_forward_scratch), batch);
+    if (L->r > (size_t)kRankPad)
+        return fail(QLC_ERR_INVALID_CONFIG, "qlc_qlora_forward_dev_noalloc handles LoRA ranks up to %d (its fixed scratch holds %d "
+                    "columns per row); got rank %zu - use qlc_qlora_forward_dev", kRankPad, kRankPad, L->r);
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(QLC_ERR_GPU, "device index %d out of range", ctx->device);
     void *scratch = g_forward_scratch_addr[ctx->device].load(std::memory_order_acquire);
     if (!scratch) {
@@ -1805,7 +1852,8 @@ int umma_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, const void 
     if (tf32 && !use_paired_ctas()) return fail(QLC_ERR_GPU, "the TF32 mode needs the paired-CTA kernel");
     if (tf32) QLC_TRY(layer_tf32_operands(L));
     const size_t es = tf32 ? 4 : 2, step = tf32 ? 32 : 64;
-    const size_t b_small = a256(batch * kRankPad * es);
+    const size_t rp = L->r_pad ? L->r_pad : (size_t)kRankPad;  // columns of the rank-padded intermediates
+    const size_t b_small = a256(batch * rp * es);
     const size_t b_part = a256((size_t)16 * (L->in_dim + L->out_dim) * kRankPad * 4);
     // The dX GEMM's last wave is only cut when nothing else would fill it (the gradient contractions do).
     static const bool cut_bwd = getenv("QLC_KCUT_BWD") != nullptr;  // diagnostics
@@ -1830,7 +1878,7 @@ int umma_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, const void 
         const DownJob down[2] = {{d_dy, L->out_dim, bt_pad, dsp}, {d_x, L->in_dim, a_pad, t1p}};
         QLC_TRY(lora_down(ctx, L, batch, down, d_gb ? 2 : 1, tf32));
         if (fork) QLC_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
-        QLC_TRY(make_map(&tDs, dsp, batch, kRankPad, 128, tf32));
+        QLC_TRY(make_map(&tDs, dsp, batch, rp, 128, tf32));
         QLC_TRY(make_map(&tA, a_pad, L->r_pad, L->in_dim, (uint32_t)step, tf32, tf32));
         a.ext_steps = (uint32_t)(L->r_pad / step);
     } else {
