@@ -45,18 +45,23 @@ extern "C" {
 #define QLC_DTYPE_F16 2 /* accepted by qlc_quantize_nf4_typed only */
 
 /* Arithmetic used by the layer GEMMs.
- *  AUTO       : tensor-core path (bf16 operands, fp32 accumulate) when the shape allows it
- *               (block_size 32, 64, 128 or 256, in_dim and out_dim multiples of 64, LoRA rank <= 64),
- *               otherwise the exact fp32 path.  Exception: the reference-named fp32 host entry points
- *               qlc_qlora_forward / qlc_qlora_backward use TF32 instead of bf16 where the shape allows it,
- *               so that they keep the reference's GPU-vs-CPU tolerances (max abs diff 1e-3 / 1e-2,
- *               qlora-wgpu/tests/gpu_parity.rs:59, gpu_backward.rs:88-96) at every shape.
+ *  AUTO       : tensor-core path (bf16 operands, fp32 accumulate) for every quantised layer with a LoRA
+ *               rank <= 256.  Layers with block_size 32, 64, 128 or 256 and in_dim / out_dim multiples of
+ *               64 run the fused kernels (the NF4 weight tile is decoded inside the GEMM); any other
+ *               dimensions or block size run through a zero-padded bf16 copy of the layer (2 bytes per
+ *               weight of extra device memory, built at the layer's first call).  Larger ranks take the
+ *               exact fp32 path.  Exception: the reference-named fp32 host entry points
+ *               qlc_qlora_forward / qlc_qlora_backward use TF32 instead of bf16 on fused-kernel shapes and
+ *               the exact fp32 path on all others, so that they keep the reference's GPU-vs-CPU
+ *               tolerances (max abs diff 1e-3 / 1e-2, qlora-wgpu/tests/gpu_parity.rs:59,
+ *               gpu_backward.rs:88-96) at every shape.
  *  FP32_EXACT : fp32 SIMT kernels that reproduce the reference's CPU accumulation order
  *               bit-for-bit (any shape, any block size).
- *  BF16       : force the tensor-core path; unsupported shapes fail with QLC_ERR_GPU.
+ *  BF16       : force the tensor-core path; a layer it does not take (rank > 256) fails with QLC_ERR_GPU.
  *  TF32       : tensor-core path with fp32 operands read as tf32 (fp32 accumulate), for a relative
- *               Frobenius error <= 1e-3; same shape limits as BF16, about half its speed.  fp32
- *               activations are consumed as they are (bf16 ones are widened first). */
+ *               Frobenius error <= 1e-3, about half the speed of BF16.  Fused-kernel shapes only: other
+ *               layers are multiplied in exact fp32 in this mode.  fp32 activations are consumed as they
+ *               are (bf16 ones are widened first). */
 #define QLC_PRECISION_AUTO 0
 #define QLC_PRECISION_FP32_EXACT 1
 #define QLC_PRECISION_BF16 2

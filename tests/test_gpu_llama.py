@@ -225,9 +225,10 @@ def test_model_tf32_mode(v):
 
 @pytest.mark.gpu
 def test_model_auto_mode_with_an_ineligible_projection(v):
-    """AUTO precision with an MLP width that is no multiple of 64: gate / up / down take the exact fp32 path, the
-    other projections the tensor cores, so the model runs the fp32-activation pipeline with the tensor-core
-    attention fed through conversions (fp32 attention output, fp32 dQ / dK / dV)."""
+    """AUTO precision with an MLP width that is no multiple of 64: the raw gate / up matrices take the exact fp32
+    path, the quantised down projection the tensor cores through its padded copy, the other projections the fused
+    tensor-core kernels; the model runs the fp32-activation pipeline with the tensor-core attention fed through
+    conversions (fp32 attention output, fp32 dQ / dK / dV)."""
     ctx = v.GpuContext(0)   # AUTO is the default
     kw = dict(hidden=128, layers=2, heads=2, kv_heads=1, intermediate=200, vocab=128)
     rank, alpha, n_seq, seq_len = 8, 16.0, 2, 150

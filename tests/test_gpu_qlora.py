@@ -169,6 +169,56 @@ def test_tensor_core_path_vs_oracle(v, oracle, tc_ctx, out_dim, in_dim, r, batch
         assert g.grad_a is None and g.grad_b is None
 
 
+@pytest.mark.parametrize("out_dim,in_dim,r,batch,block", [
+    (18, 20, 5, 3, 64),       # the reference's own GPU test shape (qlora-wgpu/tests/gpu_backward.rs:56-60)
+    (33, 20, 0, 18, 64),      # no adapter; the odd sizes of gpu_backward.rs:20-24
+    (100, 200, 96, 70, 64),   # rank above 64 on ragged dimensions
+    (130, 70, 128, 257, 64),  # ragged rows as well
+    (576, 100, 16, 300, 64),  # only in_dim ragged
+    (64, 128, 16, 7, 48),     # aligned dimensions, a block size the fused kernels do not take
+    (50, 36, 4, 40, 7),       # everything odd
+])
+def test_tensor_core_path_ragged_dimensions_and_block_sizes(v, oracle, tc_ctx, out_dim, in_dim, r, batch, block):
+    """Dimensions that are no multiple of 64 and arbitrary block sizes stay on the tensor cores (the context is
+    pinned to them, so a refusal would raise): the layer runs through a zero-padded bf16 copy of itself."""
+    layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, cfg=v.QuantConfig(block, True),
+                                             seed=out_dim + in_dim)
+    for _ in range(2):  # the second pass reuses the padded copy
+        y = layer.forward(x, batch)
+        _assert_close("forward", y, oracle.qlora_forward(x, batch, wd, out_dim, in_dim, a, b, r, alpha, threads=8), batch, out_dim)
+        g = layer.backward(x, dy, batch)
+        gx, ga, gb = oracle.qlora_backward(x, dy, batch, wd, out_dim, in_dim, a, b, r, alpha, threads=8)
+        _assert_close("grad_x", g.grad_x, gx, batch, in_dim)
+        if r:
+            _assert_close("grad_a", g.grad_a, ga, r, in_dim)
+            _assert_close("grad_b", g.grad_b, gb, out_dim, r)
+        else:
+            assert g.grad_a is None and g.grad_b is None
+
+
+def test_ragged_layer_follows_adapter_updates_and_slab_accumulation(v, oracle, tc_ctx):
+    """A ragged layer's padded copy follows set_adapter_weights, and the slab pipeline of the host entry points
+    (gradients summed slab after slab) gives the gradients of the whole batch."""
+    from vkqlora.rs_b200 import _lib
+    out_dim, in_dim, r, batch = 100, 200, 8, 2 * 2048 + 300
+    layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, seed=77)
+    layer.forward(x[:in_dim * 4], 4)  # builds the padded copy with the first adapter
+    a2, b2 = normal(91, r * in_dim, 0.05), normal(92, out_dim * r, 0.05)
+    layer.adapter_mut().set_weights(a2, b2)
+    xb, dyb = to_bf16_bits(x), to_bf16_bits(dy)
+    y = bf16_bits_to_f32(layer.forward_host(xb, batch, v.DTYPE_BF16))
+    _assert_close("forward", y, oracle.qlora_forward(x, batch, wd, out_dim, in_dim, a2, b2, r, alpha, threads=8), batch, out_dim,
+                  tol=6e-3)  # + the bf16 rounding of the returned Y
+    gx = np.empty(batch * in_dim, np.uint16)
+    ga, gb = np.empty(r * in_dim, np.float32), np.empty(out_dim * r, np.float32)
+    _lib.check(_lib.lib.qlc_qlora_backward_host(tc_ctx._h, layer._h, xb.ctypes.data, dyb.ctypes.data, v.DTYPE_BF16, batch,
+                                                gx.ctypes.data, ga.ctypes.data, gb.ctypes.data))
+    gx_ref, ga_ref, gb_ref = oracle.qlora_backward(x, dy, batch, wd, out_dim, in_dim, a2, b2, r, alpha, threads=8)
+    _assert_close("grad_x", bf16_bits_to_f32(gx), gx_ref, batch, in_dim, tol=6e-3)
+    _assert_close("grad_a", ga, ga_ref, r, in_dim)
+    _assert_close("grad_b", gb, gb_ref, out_dim, r)
+
+
 def test_tensor_core_path_plain_fp32_scales(v, oracle, tc_ctx):
     # from_raw_parts tensors carry fp32 scales (what the Python entry points rebuild)
     layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, 256, 384, 16, 128, cfg=v.QuantConfig(64, False))

@@ -662,6 +662,7 @@ static int refresh_padded_adapter(qlc_layer *L) {
     QLC_TRY(launch_pad_to_bf16(L->ctx, L->d_b, L->out_dim, L->r, L->d_b_pad, L->out_dim, L->r_pad));
     QLC_TRY(launch_pad_transpose_to_bf16(L->ctx, L->d_b, L->out_dim, L->r, L->d_bt_pad, L->r_pad, L->out_dim));
     L->pad32_valid = false;  // rebuilt by the next TF32-mode call
+    L->shadow_valid = false; // and the padded copy's adapter matrices by the next tensor-core call
     return QLC_OK;
 }
 
@@ -835,12 +836,15 @@ static int same_device(const qlc_ctx *ctx, const qlc_layer *L) {
 // Which arithmetic a call uses (see QLC_PRECISION_* in the header).
 static int pick_path(qlc_ctx *ctx, const qlc_layer *L, bool *use_umma) {
     const bool ok = umma_supported(L);
-    if (ctx->precision == QLC_PRECISION_FP32_EXACT || (!L->w && ctx->precision == QLC_PRECISION_TF32)) {
-        *use_umma = false;  // (a raw projection has no tf32 kernels: TF32 mode multiplies it in exact fp32)
+    if (ctx->precision == QLC_PRECISION_FP32_EXACT ||
+        (ctx->precision == QLC_PRECISION_TF32 && (!L->w || !umma_fused_supported(L)))) {
+        // TF32 exists in the fused kernels only: raw projections and layers that run through a padded copy are
+        // multiplied in exact fp32 in that mode (more precise than asked for, slower)
+        *use_umma = false;
     } else if (ctx->precision == QLC_PRECISION_BF16 || ctx->precision == QLC_PRECISION_TF32) {
         if (!ok)
             return fail(QLC_ERR_GPU,
-                        "tensor-core path needs block_size 32, 64, 128 or 256, in_dim/out_dim multiples of 64 and rank <= 256 "
+                        "the tensor-core path takes LoRA ranks up to 256 and dimensions below 2^30 "
                         "(got block %zu, in %zu, out %zu, r %zu)",
                         L->w ? L->w->block_size : (size_t)0, L->in_dim, L->out_dim, L->r);
         *use_umma = true;
@@ -903,7 +907,7 @@ int qlc_qlora_forward_dev_noalloc(qlc_ctx *ctx, qlc_layer *L, const void *d_x, s
     QLC_TRY(same_device(ctx, L));
     if (batch == 0 || L->out_dim == 0) return QLC_OK;
     if (!d_x || !d_y) return fail(QLC_ERR_INVALID_CONFIG, "null buffer");
-    if (!L->w || !umma_supported(L))
+    if (!L->w || !umma_fused_supported(L))
         return fail(QLC_ERR_INVALID_CONFIG,
                     "qlc_qlora_forward_dev_noalloc needs a tensor-core-eligible layer (block_size 32, 64, 128 or 256, in_dim and "
                     "out_dim multiples of 64, rank <= 64); got block %zu, in %zu, out %zu, r %zu",
@@ -1131,7 +1135,8 @@ static int fused_submit(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *d
     QLC_CUDA(cudaSetDevice(ctx->device));
     bool use_umma = false;
     QLC_TRY(pick_path(ctx, L, &use_umma));
-    if (!use_umma || dtype != QLC_DTYPE_BF16 || batch < 2 * kSlabRows || ctx->precision == QLC_PRECISION_TF32 || !L->w) {
+    if (!use_umma || dtype != QLC_DTYPE_BF16 || batch < 2 * kSlabRows || ctx->precision == QLC_PRECISION_TF32 || !L->w ||
+        !umma_fused_supported(L)) {
         // no pipelined form for this case: the two stateless calls, one after the other
         QLC_TRY(qlc_qlora_forward_host(ctx, L, x, dtype, batch, y));
         return qlc_qlora_backward_host(ctx, L, x, dy, dtype, batch, grad_x, grad_a, grad_b);
@@ -1233,7 +1238,7 @@ struct Fp32CallPrecision {
     qlc_ctx *ctx;
     int saved;
     Fp32CallPrecision(qlc_ctx *c, const qlc_layer *L) : ctx(c), saved(c->precision) {
-        if (saved == QLC_PRECISION_AUTO) ctx->precision = umma_supported(L) ? QLC_PRECISION_TF32 : QLC_PRECISION_FP32_EXACT;
+        if (saved == QLC_PRECISION_AUTO) ctx->precision = umma_fused_supported(L) ? QLC_PRECISION_TF32 : QLC_PRECISION_FP32_EXACT;
     }
     ~Fp32CallPrecision() { ctx->precision = saved; }
 };

@@ -131,6 +131,10 @@ struct qlc_layer {
     float *d_grad_bucket = nullptr;  // r*in_dim + out_dim*r fp32
     // Cached tensor maps (opaque blobs, built lazily by the tensor-core path).
     void *tmaps = nullptr;
+    // Layers the fused kernels do not take (dimensions no multiple of 64, other block sizes): a padded bf16 copy of
+    // the layer, built at the first tensor-core call (umma_gemm.cu); its adapter copies follow every change of A / B.
+    qlc_layer *shadow = nullptr;
+    bool shadow_valid = false;
 };
 
 namespace qlc {
@@ -168,7 +172,8 @@ int exact_qlora_backward(qlc_ctx *ctx, qlc_layer *layer, const float *d_x, const
                          float *d_gx, float *d_ga, float *d_gb);
 
 // umma_gemm.cu — tcgen05 / TMEM / TMA tensor-core path
-bool umma_supported(const qlc_layer *layer);
+bool umma_supported(const qlc_layer *layer);        // the tensor-core path takes this layer (fused kernels or padded copy)
+bool umma_fused_supported(const qlc_layer *layer);  // ... through the fused kernels (TF32 needs these)
 int umma_qlora_forward(qlc_ctx *ctx, qlc_layer *layer, const void *d_x, size_t batch, void *d_y, int y_dtype,
                        bool tf32 = false);
 // accumulate != 0: grad_a / grad_b receive this slab's contribution on top of their current contents.

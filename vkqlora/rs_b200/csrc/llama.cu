@@ -977,7 +977,7 @@ bool wants_pipeline(const qlc_llama *m) {
     if (off || m->cfg.hidden % 64 || m->cfg.intermediate % 64) return false;
     for (const LlamaLayer &L : m->layers)
         for (const qlc_layer *p : L.proj)
-            if (!p || !umma_supported(p)) return false;
+            if (!p || !umma_fused_supported(p)) return false;
     return true;
 }
 
@@ -1682,6 +1682,7 @@ static int train_step_impl(qlc_llama *m, qlc_adam *adam, qlc_comm *comm, const u
     QLC_TRY(qlc_adam_step_dev(adam, params.size(), params.data(), grads.data(), lens.data(), nullptr));
     // the bf16 operand copies of all adapters, rebuilt in one launch per 64 adapters
     QLC_TRY(launch_refresh_adapters(m->ctx, updated.data(), updated.size()));
+    for (qlc_layer *L : updated) L->shadow_valid = false;
     const auto t_sub = std::chrono::steady_clock::now();
     const int st_sync = sync(m);
     if (host_timing) {

@@ -1507,14 +1507,15 @@ inline size_t a256(size_t b) { return (b + 255) & ~(size_t)255; }
 
 GemmArgs base_args(qlc_ctx *ctx, const qlc_layer *L) {
     GemmArgs a{};
-    const qlc_qtensor *q = L->w;
-    a.codes = q->d_codes;
-    a.absmax_codes = q->d_absmax_codes;
-    a.absmax2 = q->d_absmax2;
-    a.scales_f32 = q->d_scales_f32;
-    a.blk_shift = 5;
-    while (((size_t)1 << a.blk_shift) < q->block_size) ++a.blk_shift;
-    a.dq = q->dq ? 1 : 0;
+    if (const qlc_qtensor *q = L->w) {  // (a layer with a plain bf16 weight has no NF4 operand to describe)
+        a.codes = q->d_codes;
+        a.absmax_codes = q->d_absmax_codes;
+        a.absmax2 = q->d_absmax2;
+        a.scales_f32 = q->d_scales_f32;
+        a.blk_shift = 5;
+        while (((size_t)1 << a.blk_shift) < q->block_size) ++a.blk_shift;
+        a.dq = q->dq ? 1 : 0;
+    }
     a.w_rows = (uint32_t)L->out_dim;
     a.w_cols = (uint32_t)L->in_dim;
     a.splits = 1;
@@ -1537,6 +1538,37 @@ uint32_t pick_splits(uint32_t token_steps, uint32_t tiles, uint32_t slots) {
 // Plain tensor-core GEMM on bf16 operands, fp32 (or, with c_bf16, bf16) result: C (M, N) = A (M, K) · op(B), K a multiple of 64.
 //   b_is_kn == false: B is (N, K) row-major (C = A·B^T);  b_is_kn == true: B is (K, N) row-major (C = A·B).
 // Both operands come through TMA (single-CTA kernel, 256x256 tiles).  Used for the tied LM head of the model.
+// ext (optional): `ext_steps` further 64-deep steps appended to the contraction, whose A operand comes through
+// *tAe (a (M, 64*ext_steps) bf16 matrix, boxes of 128 rows) and whose B operand through *tBe ((N, 64*ext_steps) with
+// boxes of 256 rows when !b_is_kn, (64*ext_steps, N) with boxes of 64 rows when b_is_kn): the LoRA term.
+static int umma_gemm_bf16_ext(qlc_ctx *ctx, const __nv_bfloat16 *d_a, const __nv_bfloat16 *d_b, bool b_is_kn, void *d_c,
+                              size_t M, size_t N, size_t K, bool c_bf16, const CUtensorMap *tAe, const CUtensorMap *tBe,
+                              uint32_t ext_steps, int prof_slot) {
+    if (M == 0 || N == 0) return QLC_OK;
+    if (K == 0 || K % 64 || N % 32 || M >= (1u << 30) || N >= (1u << 30))
+        return fail(QLC_ERR_GPU, "tensor-core GEMM needs K a multiple of 64 and N a multiple of 32 (M %zu, N %zu, K %zu)", M, N, K);
+    CUtensorMap tA, tB;
+    QLC_TRY(make_map(&tA, d_a, M, K, 128));
+    GemmArgs a{};
+    a.splits = 1;
+    a.a_rows = 256;
+    a.out_scale = 1.0f;
+    a.status = ctx->d_status;
+    a.M = (uint32_t)M;
+    a.N = (uint32_t)N;
+    a.k_steps = (uint32_t)(K / 64);
+    a.ext_steps = ext_steps;
+    a.out = d_c;
+    a.ldo = (uint32_t)N;
+    a.out_bf16 = c_bf16 ? 1 : 0;
+    if (!b_is_kn) {
+        QLC_TRY(make_map(&tB, d_b, N, K, 256));
+        return launch_gemm<256, 2, false, false, false, 3>(ctx, prof_slot, tA, tB, ext_steps ? *tAe : tA, ext_steps ? *tBe : tB, a);
+    }
+    QLC_TRY(make_map(&tB, d_b, K, N, 64));
+    return launch_gemm<256, 2, false, true, false, 3>(ctx, prof_slot, tA, tB, ext_steps ? *tAe : tA, ext_steps ? *tBe : tB, a);
+}
+
 int umma_gemm_bf16(qlc_ctx *ctx, const __nv_bfloat16 *d_a, const __nv_bfloat16 *d_b, bool b_is_kn, void *d_c, size_t M,
                    size_t N, size_t K, bool c_bf16) {
     if (M == 0 || N == 0) return QLC_OK;
@@ -1574,17 +1606,37 @@ bool pdl_enabled() {
     return on;
 }
 
-bool umma_supported(const qlc_layer *L) {
-    if (!L->w)  // raw projection: plain bf16 GEMMs, both operands by TMA
-        return L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
-               L->in_dim < (1u << 30) && L->out_dim < (1u << 30);
+// The fused kernels (weight tile dequantised inside the GEMM) take quantisation blocks of 32, 64, 128 or 256
+// elements and dimensions that are multiples of 64; a raw projection needs the same dimensions for its TMA-fed GEMMs.
+bool umma_fused_supported(const qlc_layer *L) {
+    const bool dims_ok = L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
+                         L->in_dim < (1u << 30) && L->out_dim < (1u << 30) && L->r <= (size_t)kMaxRank;
+    if (!L->w) return dims_ok;
     const qlc_qtensor *q = L->w;
     const bool block_ok = q->block_size == 32 || q->block_size == 64 || q->block_size == 128 || q->block_size == 256;
-    return block_ok && L->in_dim % 64 == 0 && L->out_dim % 64 == 0 && L->in_dim > 0 && L->out_dim > 0 &&
-           L->r <= (size_t)kMaxRank && L->in_dim < (1u << 30) && L->out_dim < (1u << 30);
+    return block_ok && dims_ok;
+}
+// Every other quantised layer (any block size, any dimensions - the reference's GEMMs take any (m, n, k),
+// qlora-wgpu/shaders/gemm.wgsl:14-15) reaches the tensor cores through a padded copy: see shadow_layer.
+bool umma_supported(const qlc_layer *L) {
+    if (umma_fused_supported(L)) return true;
+    return L->w != nullptr && L->in_dim > 0 && L->out_dim > 0 && L->in_dim < (1u << 30) - 64 && L->out_dim < (1u << 30) - 64 &&
+           L->r <= (size_t)kMaxRank;
 }
 
-void umma_layer_release(qlc_layer *) {}
+// Frees what this file attached to a layer: the padded copy (shadow_layer).
+void umma_layer_release(qlc_layer *L) {
+    qlc_layer *S = L->shadow;
+    if (!S) return;
+    cudaFree(S->d_w_raw_bf16);
+    cudaFree(S->d_a_pad);
+    cudaFree(S->d_b_pad);
+    cudaFree(S->d_bt_pad);
+    cudaFree(S->d_grad_bucket);
+    delete S;
+    L->shadow = nullptr;
+    L->shadow_valid = false;
+}
 
 // out (batch, 64) bf16 = s * Src·Low^T, zero beyond the rank: Src is (batch, cols) activations, Low the
 // rank-padded (r_pad, cols) bf16 adapter matrix (A_pad for T1 = X·A^T, B^T_pad for Ds = dY·B).
@@ -1739,13 +1791,154 @@ static int token_contract(qlc_ctx *ctx, qlc_layer *L, size_t batch, const Contra
                 : token_contract_t<false>(ctx, L, batch, jobs, n_jobs, partial, accumulate, stream);
 }
 
+// ---- layers the fused kernels do not take (dimensions that are no multiple of 64, other block sizes) ------------
+// Such a layer keeps a PADDED COPY of itself: the dequantised weight rounded to bf16 (the value the fused
+// producers would build, quant.rs:157-167 then one rounding) in an (out_pad, in_pad) matrix, and its adapter
+// matrices padded the same way, both dimensions rounded up to multiples of 64 with zeros.  Calls then pad the
+// activations into scratch buffers, run the plain TMA-fed tensor-core GEMMs (with the LoRA term as extension
+// steps) and the side products at the padded size, and copy the real rows and columns out.  The zeros add
+// nothing to any product.  Cost: 2 bytes per weight of extra device memory for these layers only, and two
+// strided copies per call; the fused path of aligned layers is untouched.
+static size_t pad64(size_t v) { return (v + 63) / 64 * 64; }
+
+static int shadow_refresh_adapter(qlc_layer *L) {
+    qlc_layer *S = L->shadow;
+    if (!S || L->r == 0) return QLC_OK;
+    QLC_TRY(launch_pad_to_bf16(L->ctx, L->d_a, L->r, L->in_dim, S->d_a_pad, S->r_pad, S->in_dim));
+    QLC_TRY(launch_pad_to_bf16(L->ctx, L->d_b, L->out_dim, L->r, S->d_b_pad, S->out_dim, S->r_pad));
+    return launch_pad_transpose_to_bf16(L->ctx, L->d_b, L->out_dim, L->r, S->d_bt_pad, S->r_pad, S->out_dim);
+}
+
+static int shadow_layer(qlc_ctx *ctx, qlc_layer *L, qlc_layer **out) {
+    if (L->shadow) {
+        if (!L->shadow_valid) {
+            QLC_TRY(shadow_refresh_adapter(L));
+            L->shadow_valid = true;
+        }
+        *out = L->shadow;
+        return QLC_OK;
+    }
+    const size_t in_pad = pad64(L->in_dim), out_pad = pad64(L->out_dim), n = L->out_dim * L->in_dim;
+    qlc_layer *S = new (std::nothrow) qlc_layer();
+    if (!S) return fail(QLC_ERR_GPU, "out of host memory");
+    S->ctx = L->ctx;  // borrowed: the padded copy lives and dies with its layer and takes no reference
+    S->in_dim = in_pad;
+    S->out_dim = out_pad;
+    S->r = L->r;
+    S->alpha = L->alpha;
+    S->r_pad = L->r_pad;
+    int st = QLC_OK;
+    auto chk = [&](cudaError_t e, const char *what) {
+        if (e != cudaSuccess && st == QLC_OK) st = fail(QLC_ERR_GPU, "%s: %s", what, cudaGetErrorString(e));
+    };
+    float *wide = nullptr;
+    chk(cudaMalloc(reinterpret_cast<void **>(&S->d_w_raw_bf16), (out_pad * in_pad + 8) * 2), "cudaMalloc(padded weight)");
+    chk(cudaMalloc(reinterpret_cast<void **>(&wide), (n + 4) * 4), "cudaMalloc(dequantised weight)");
+    if (L->r) {
+        chk(cudaMalloc(reinterpret_cast<void **>(&S->d_a_pad), (S->r_pad * in_pad + 8) * 2), "cudaMalloc(padded A)");
+        chk(cudaMalloc(reinterpret_cast<void **>(&S->d_b_pad), (out_pad * S->r_pad + 8) * 2), "cudaMalloc(padded B)");
+        chk(cudaMalloc(reinterpret_cast<void **>(&S->d_bt_pad), (out_pad * S->r_pad + 8) * 2), "cudaMalloc(padded B^T)");
+        chk(cudaMalloc(reinterpret_cast<void **>(&S->d_grad_bucket), (L->r * in_pad + out_pad * L->r + 4) * 4), "cudaMalloc(padded gradients)");
+    }
+    if (st == QLC_OK && L->r)
+        chk(cudaMemsetAsync(S->d_grad_bucket, 0, (L->r * in_pad + out_pad * L->r) * 4, L->ctx->stream), "cudaMemsetAsync");
+    if (st == QLC_OK) st = launch_dequantize(L->ctx, L->w, wide, QLC_DTYPE_F32);
+    if (st == QLC_OK) st = launch_pad_to_bf16(L->ctx, wide, L->out_dim, L->in_dim, S->d_w_raw_bf16, out_pad, in_pad);
+    L->shadow = S;
+    if (st == QLC_OK) st = shadow_refresh_adapter(L);
+    cudaStreamSynchronize(L->ctx->stream);
+    cudaFree(wide);
+    if (st != QLC_OK) {
+        umma_layer_release(L);
+        return st;
+    }
+    L->shadow_valid = true;
+    (void)ctx;
+    *out = S;
+    return QLC_OK;
+}
+
+// (rows, cols) -> the top-left corner of a zero-filled (rows, cols_pad) scratch matrix, 2-byte elements
+static int pad_rows_bf16(qlc_ctx *ctx, const __nv_bfloat16 *src, size_t rows, size_t cols, size_t cols_pad, __nv_bfloat16 **out) {
+    __nv_bfloat16 *p = nullptr;
+    QLC_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&p), a256(rows * cols_pad * 2), ctx->stream));
+    if (cols_pad != cols) QLC_CUDA(cudaMemsetAsync(p, 0, rows * cols_pad * 2, ctx->stream));
+    QLC_CUDA(cudaMemcpy2DAsync(p, cols_pad * 2, src, cols * 2, cols * 2, rows, cudaMemcpyDeviceToDevice, ctx->stream));
+    *out = p;
+    return QLC_OK;
+}
+
+static int shadow_forward(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *d_x, size_t batch, void *d_y, int y_dtype) {
+    qlc_layer *S = nullptr;
+    QLC_TRY(shadow_layer(ctx, L, &S));
+    const size_t es = y_dtype == QLC_DTYPE_BF16 ? 2 : 4;
+    __nv_bfloat16 *xp = nullptr;
+    void *yp = nullptr;
+    QLC_TRY(pad_rows_bf16(ctx, d_x, batch, L->in_dim, S->in_dim, &xp));
+    QLC_CUDA(cudaMallocAsync(&yp, a256(batch * S->out_dim * es), ctx->stream));
+    int st = umma_qlora_forward(ctx, S, xp, batch, yp, y_dtype, false);
+    if (st == QLC_OK && cudaMemcpy2DAsync(d_y, L->out_dim * es, yp, S->out_dim * es, L->out_dim * es, batch,
+                                          cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+        st = fail(QLC_ERR_GPU, "copy out of the padded result failed");
+    cudaFreeAsync(xp, ctx->stream);
+    cudaFreeAsync(yp, ctx->stream);
+    return st;
+}
+
+static int shadow_backward(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *d_x, const __nv_bfloat16 *d_dy, size_t batch,
+                           void *d_gx, int gx_dtype, float *d_ga, float *d_gb, int accumulate) {
+    qlc_layer *S = nullptr;
+    QLC_TRY(shadow_layer(ctx, L, &S));
+    const size_t es = gx_dtype == QLC_DTYPE_BF16 ? 2 : 4;
+    __nv_bfloat16 *xp = nullptr, *dyp = nullptr;
+    void *gxp = nullptr;
+    QLC_TRY(pad_rows_bf16(ctx, d_x, batch, L->in_dim, S->in_dim, &xp));
+    QLC_TRY(pad_rows_bf16(ctx, d_dy, batch, L->out_dim, S->out_dim, &dyp));
+    QLC_CUDA(cudaMallocAsync(&gxp, a256(batch * S->in_dim * es), ctx->stream));
+    // padded gradients: (r, in_pad) and (out_pad, r)
+    float *gap = (L->r && d_ga) ? S->d_grad_bucket : nullptr;
+    float *gbp = (L->r && d_gb) ? S->d_grad_bucket + L->r * S->in_dim : nullptr;
+    int st = QLC_OK;
+    auto copy2d = [&](void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t rows) {
+        if (st == QLC_OK && rows && width &&
+            cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, rows, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+            st = fail(QLC_ERR_GPU, "copy to or from a padded buffer failed");
+    };
+    if (accumulate) {  // the running sums go in, so that the padded products add to them
+        if (gap) copy2d(gap, S->in_dim * 4, d_ga, L->in_dim * 4, L->in_dim * 4, L->r);
+        if (gbp) copy2d(gbp, L->r * 4, d_gb, L->r * 4, L->r * 4, L->out_dim);
+    }
+    if (st == QLC_OK) st = umma_qlora_backward(ctx, S, xp, dyp, batch, gxp, gx_dtype, gap, gbp, accumulate, false);
+    copy2d(d_gx, L->in_dim * es, gxp, S->in_dim * es, L->in_dim * es, batch);
+    if (gap) copy2d(d_ga, L->in_dim * 4, gap, S->in_dim * 4, L->in_dim * 4, L->r);
+    if (gbp) copy2d(d_gb, L->r * 4, gbp, L->r * 4, L->r * 4, L->out_dim);
+    cudaFreeAsync(xp, ctx->stream);
+    cudaFreeAsync(dyp, ctx->stream);
+    cudaFreeAsync(gxp, ctx->stream);
+    return st;
+}
+
 // d_x: (batch, in_dim) bf16, or fp32 when tf32.
 int umma_qlora_forward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, size_t batch, void *d_y, int y_dtype, bool tf32) {
     if (batch >= (1u << 31) / 2) return fail(QLC_ERR_GPU, "batch too large for the tensor-core path");
-    if (!L->w) {  // raw projection: Y = X·W^T with the bf16 copy of the weight
+    if (L->w && !umma_fused_supported(L)) {
+        if (tf32) return fail(QLC_ERR_GPU, "internal: the padded-copy path has no tf32 form");
+        return shadow_forward(ctx, L, static_cast<const __nv_bfloat16 *>(d_x), batch, d_y, y_dtype);
+    }
+    if (!L->w) {  // plain bf16 weight (a raw projection, or the padded copy of a layer): Y = X·W^T (+ LoRA term)
         if (tf32) return fail(QLC_ERR_GPU, "internal: raw projections have no tf32 path");
-        return umma_gemm_bf16(ctx, static_cast<const __nv_bfloat16 *>(d_x), L->d_w_raw_bf16, false, d_y, batch, L->out_dim,
-                              L->in_dim, y_dtype == QLC_DTYPE_BF16);
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(d_x);
+        if (L->r == 0)
+            return umma_gemm_bf16(ctx, x, L->d_w_raw_bf16, false, d_y, batch, L->out_dim, L->in_dim, y_dtype == QLC_DTYPE_BF16);
+        void *ws = nullptr;
+        QLC_TRY(ctx_workspace(ctx, a256(batch * L->r_pad * 2), &ws));
+        const DownJob job{x, L->in_dim, L->d_a_pad, ws};  // T1p = s·X·A^T
+        QLC_TRY(lora_down(ctx, L, batch, &job, 1, false));
+        CUtensorMap tT1, tB;
+        QLC_TRY(make_map(&tT1, ws, batch, L->r_pad, 128));
+        QLC_TRY(make_map(&tB, L->d_b_pad, L->out_dim, L->r_pad, 256));
+        return umma_gemm_bf16_ext(ctx, x, L->d_w_raw_bf16, false, d_y, batch, L->out_dim, L->in_dim, y_dtype == QLC_DTYPE_BF16,
+                                  &tT1, &tB, (uint32_t)(L->r_pad / 64), 0);
     }
     if (tf32 && !use_paired_ctas()) return fail(QLC_ERR_GPU, "the TF32 mode needs the paired-CTA kernel");
     if (tf32) QLC_TRY(layer_tf32_operands(L));
@@ -1844,10 +2037,35 @@ int umma_qlora_forward_noalloc(qlc_ctx *ctx, qlc_layer *L, const __nv_bfloat16 *
 int umma_qlora_backward(qlc_ctx *ctx, qlc_layer *L, const void *d_x, const void *d_dy, size_t batch, void *d_gx,
                         int gx_dtype, float *d_ga, float *d_gb, int accumulate, bool tf32) {
     if (batch >= (1u << 31) / 2) return fail(QLC_ERR_GPU, "batch too large for the tensor-core path");
-    if (!L->w) {  // raw projection: dX = dY·W with the bf16 copy of the weight; no adapter, no adapter gradients
+    if (L->w && !umma_fused_supported(L)) {
+        if (tf32) return fail(QLC_ERR_GPU, "internal: the padded-copy path has no tf32 form");
+        return shadow_backward(ctx, L, static_cast<const __nv_bfloat16 *>(d_x), static_cast<const __nv_bfloat16 *>(d_dy), batch,
+                               d_gx, gx_dtype, d_ga, d_gb, accumulate);
+    }
+    if (!L->w) {  // plain bf16 weight: dX = dY·W (+ Ds·A), and the adapter gradients as in the fused path
         if (tf32) return fail(QLC_ERR_GPU, "internal: raw projections have no tf32 path");
-        return umma_gemm_bf16(ctx, static_cast<const __nv_bfloat16 *>(d_dy), L->d_w_raw_bf16, true, d_gx, batch, L->in_dim,
-                              L->out_dim, gx_dtype == QLC_DTYPE_BF16);
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(d_x), *dy = static_cast<const __nv_bfloat16 *>(d_dy);
+        if (L->r == 0)
+            return umma_gemm_bf16(ctx, dy, L->d_w_raw_bf16, true, d_gx, batch, L->in_dim, L->out_dim, gx_dtype == QLC_DTYPE_BF16);
+        const size_t b_small = a256(batch * L->r_pad * 2);
+        const size_t b_part = a256((size_t)16 * (L->in_dim + L->out_dim) * kRankPad * 4);
+        void *ws = nullptr;
+        QLC_TRY(ctx_workspace(ctx, 2 * b_small + b_part, &ws));
+        void *t1p = ws, *dsp = static_cast<char *>(ws) + b_small;
+        float *partial = reinterpret_cast<float *>(static_cast<char *>(ws) + 2 * b_small);
+        const DownJob down[2] = {{dy, L->out_dim, L->d_bt_pad, dsp}, {x, L->in_dim, L->d_a_pad, t1p}};  // Ds, T1
+        QLC_TRY(lora_down(ctx, L, batch, down, d_gb ? 2 : 1, false));
+        CUtensorMap tDs, tA;
+        QLC_TRY(make_map(&tDs, dsp, batch, L->r_pad, 128));
+        QLC_TRY(make_map(&tA, L->d_a_pad, L->r_pad, L->in_dim, 64));
+        QLC_TRY(umma_gemm_bf16_ext(ctx, dy, L->d_w_raw_bf16, true, d_gx, batch, L->in_dim, L->out_dim, gx_dtype == QLC_DTYPE_BF16,
+                                   &tDs, &tA, (uint32_t)(L->r_pad / 64), 1));
+        ContractJob jobs[2];
+        int n = 0;
+        if (d_ga) jobs[n++] = ContractJob{x, L->in_dim, dsp, 1, d_ga};    // dA = Ds^T·X
+        if (d_gb) jobs[n++] = ContractJob{dy, L->out_dim, t1p, 0, d_gb};  // dB = dY^T·T1s
+        if (n) QLC_TRY(token_contract(ctx, L, batch, jobs, n, partial, accumulate, ctx->stream, false));
+        return QLC_OK;
     }
     if (tf32 && !use_paired_ctas()) return fail(QLC_ERR_GPU, "the TF32 mode needs the paired-CTA kernel");
     if (tf32) QLC_TRY(layer_tf32_operands(L));
