@@ -415,7 +415,7 @@ def ours_arm(args, dist_):
     achieved = (fl_launch * gemm_launches / (gemm_ms * 1e-3) / 1e12) if gemm_ms > 0 else 0.0
     # the timed region is tens of milliseconds: the burst figure is the denominator; the sustained one beside it
     roofline = {
-        "bound": "tensor", "kernel": "umma_gemm2_kernel (paired-CTA tcgen05 weight GEMMs: forward Y and backward dX)",
+        "bound": "tensor", "kernel": "umma_gemm3_kernel (persistent paired-CTA tcgen05 weight GEMMs: forward Y and backward dX)",
         "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
         "frac": achieved / peaks["tflops_burst"], "peak_source": f"bf16_tflops (burst), {peaks['source']}",
         "frac_sustained": achieved / peaks["tflops_sustained"], "peak_sustained": peaks["tflops_sustained"],
@@ -657,7 +657,7 @@ def measure_stack(v, dist_, steps, warmup):
         "workload": C5_WORKLOAD, "scaling": "strong", "metric": METRIC, "value": C5_TOKENS / (ms_step * 1e-3), "unit": UNIT,
         "ms_per_step": ms_step, "steps": steps, "warmup": warmup, "tokens_per_gpu": rows, "global_tokens": C5_TOKENS,
         "tflops_per_gpu": tfl, "flops_per_step_per_gpu": flops_rank, **frac_of(tfl, peaks, "tflops_sustained"),
-        "gemm_roofline": {"bound": "tensor", "kernel": "umma_gemm2_kernel (all projections, forward Y and backward dX)",
+        "gemm_roofline": {"bound": "tensor", "kernel": "umma_gemm3_kernel (all projections, forward Y and backward dX)",
                           "achieved": achieved, "unit": "TFLOP/s", **frac_of(achieved, peaks, "tflops_sustained"),
                           "per_slot_ms_per_step": {name: prof[k][0] / n_prof for k, name in
                                                    enumerate(("fwd_gemm", "bwd_dx_gemm", "lora_down", "token_grads"))}},
@@ -843,8 +843,9 @@ def measure_quant_sweep(v, dist_, sizes, iters):
         copies = max(1, (512 << 20) // (4 * n))  # rotate inputs so every launch reads cold data
         ws = [torch.randn(n, device=dev, dtype=torch.float32) * 0.02 for _ in range(copies)]
         qs = [v.QuantizedTensor.quantize_dev(w.data_ptr(), n_side, n_side, v.QuantConfig(), ctx) for w in ws]
-        of = torch.empty(n, device=dev, dtype=torch.float32)
-        ob = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        # outputs rotate as well: a single 64 MiB output would stay in the 126 MB L2 from one launch to the next
+        ofs = [torch.empty(n, device=dev, dtype=torch.float32) for _ in range(copies)]
+        obs = [torch.empty(n, device=dev, dtype=torch.bfloat16) for _ in range(max(1, (512 << 20) // (2 * n)))]
         ctx.synchronize()
         torch.cuda.synchronize()
 
@@ -866,8 +867,8 @@ def measure_quant_sweep(v, dist_, sizes, iters):
         tq = timed(lambda i: qs[i % copies].requantize_dev(ws[(i + 1) % copies].data_ptr()), it)
         for i in range(copies):  # restore: tensor i holds weights i again
             qs[i].requantize_dev(ws[i].data_ptr())
-        tf = timed(lambda i: qs[i % copies].dequantize_dev(of.data_ptr(), v.DTYPE_F32), it)
-        tb = timed(lambda i: qs[i % copies].dequantize_dev(ob.data_ptr(), v.DTYPE_BF16), it)
+        tf = timed(lambda i: qs[i % copies].dequantize_dev(ofs[i % copies].data_ptr(), v.DTYPE_F32), it)
+        tb = timed(lambda i: qs[i % copies].dequantize_dev(obs[i % len(obs)].data_ptr(), v.DTYPE_BF16), it)
         bq, bf_, bb = 4.515869140625 * n, 4.515869140625 * n, 2.515869140625 * n
         hb = peaks["hbm_gbs"]
         out[f"{n_side}x{n_side}"] = {
@@ -875,12 +876,12 @@ def measure_quant_sweep(v, dist_, sizes, iters):
             "dequant_f32_us": tf * 1e6, "dequant_f32_gbs": bf_ / tf / 1e9, "dequant_f32_frac": bf_ / tf / 1e9 / hb,
             "dequant_bf16_us": tb * 1e6, "dequant_bf16_gbs": bb / tb / 1e9, "dequant_bf16_frac": bb / tb / 1e9 / hb,
             "launches_timed": it}
-        del ws, qs, of, ob
+        del ws, qs, ofs, obs
         torch.cuda.empty_cache()
     clocks = sampler.stop(t_begin, time.perf_counter())
     return {"workload": "quantize_nf4 / dequantize sweep, fp32 weights ~N(0,0.02), block 64 + double quant",
             "unit": "GB/s of algorithmic bytes (quantize 4.51587 B/elem; dequantize 0.51587 + 4 (fp32) or + 2 (bf16) B/elem)",
-            "l2": "inputs rotate over >= 512 MiB of distinct buffers", "bound": "hbm", "peak": peaks["hbm_gbs"],
+            "l2": "inputs and outputs rotate over >= 512 MiB of distinct buffers each", "bound": "hbm", "peak": peaks["hbm_gbs"],
             "peak_source": f"hbm_gbs, {peaks['source']}", "sizes": out, "clocks": clocks}
 
 

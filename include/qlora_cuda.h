@@ -228,8 +228,10 @@ int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *layer, const void *x, const
  * a backward pass replayed with a stored upstream gradient): the same results as qlc_qlora_forward_host followed
  * by qlc_qlora_backward_host, but X crosses the host link once instead of twice and one row-slab pipeline
  * (copy in | forward + backward | copy out) serves both passes.  The reference's two stateless calls upload X
- * twice (qlora-wgpu/src/kernels.rs:262-267 and 301-307 each take x); those calls remain.  grad_a / grad_b may be
- * NULL: the gradients then stay in the layer's device bucket (qlc_layer_grad_bucket), e.g. for an all-reduce. */
+ * twice (qlora-wgpu/src/kernels.rs:262-267 and 301-307 each take x); those calls remain.  grad_a / grad_b may
+ * both be NULL: the gradients then go to the layer's device bucket (qlc_layer_grad_bucket) and stay there, e.g.
+ * for an all-reduce; with a host pointer given the pipelined form accumulates them in its own staging memory and
+ * leaves the layer's bucket alone. */
 int qlc_qlora_forward_backward_host(qlc_ctx *ctx, qlc_layer *layer, const void *x, const void *dy, int dtype,
                                     size_t batch, void *y, void *grad_x, float *grad_a, float *grad_b);
 /* The same call without waiting: it returns once the copies and kernels are queued and hands out a ticket;

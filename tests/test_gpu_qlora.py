@@ -353,7 +353,7 @@ def test_fused_forward_backward_host_equals_the_two_stateless_calls(v, oracle, t
 def test_async_fused_host_calls_two_in_flight(v, oracle, tc_ctx):
     """qlc_qlora_forward_backward_host_async: three submissions with different inputs, two in flight at a time
     (each with its own pinned host buffers), waited for by ticket.  Every result equals the synchronous call's:
-    a submission must not overwrite staged inputs or outputs that its predecessor still needs."""
+    a submission must not overwrite staged inputs or outputs that an earlier one still needs."""
     import torch
     out_dim, in_dim, r, batch = 320, 256, 8, 5120 + 300
     layer, wd, x0, dy0, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, seed=46)
@@ -391,7 +391,9 @@ def test_async_fused_host_calls_two_in_flight(v, oracle, tc_ctx):
     for i, y, gx, ga, gb in results:
         _, _, y_ref, g_ref = cases[i]
         assert np.array_equal(y, y_ref) and np.array_equal(gx, g_ref.grad_x), i
-        assert np.array_equal(ga, g_ref.grad_a) and np.array_equal(gb, g_ref.grad_b), i
+        # the asynchronous call splits the batch into equal slabs, the synchronous one ramps them: grad_A / grad_B are
+        # summed slab after slab in fp32, so the two agree to fp32 rounding
+        assert rel_fro(ga, g_ref.grad_a) <= 1e-5 and rel_fro(gb, g_ref.grad_b) <= 1e-5, i
     with pytest.raises(v.InvalidConfig):
         tc_ctx.wait(10**6)
 

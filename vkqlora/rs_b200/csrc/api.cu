@@ -72,8 +72,26 @@ int ctx_tile_counters(qlc_ctx *ctx, int set, size_t count, int **out) {
     return QLC_OK;
 }
 
+// Waits (on the host) until the copies of earlier asynchronous host-buffer submissions have ended: they run on the
+// copy streams, which the context's main stream does not cover.
+static int fused_quiesce(qlc_ctx *ctx) {
+    if (!ctx->fused_open) return QLC_OK;
+    QLC_CUDA(cudaStreamSynchronize(ctx->copy_stream));
+    QLC_CUDA(cudaStreamSynchronize(ctx->d2h_stream));
+    ctx->fused_open = false;
+    return QLC_OK;
+}
+
+static int ctx_io_grow(qlc_ctx *ctx, size_t bytes);
 int ctx_io(qlc_ctx *ctx, size_t bytes, void **out) {
+    QLC_TRY(fused_quiesce(ctx));  // the staging area is about to be reused by a synchronous entry point
+    QLC_TRY(ctx_io_grow(ctx, bytes));
+    *out = ctx->io;
+    return QLC_OK;
+}
+static int ctx_io_grow(qlc_ctx *ctx, size_t bytes) {
     if (bytes > ctx->io_bytes) {
+        QLC_TRY(fused_quiesce(ctx));
         QLC_CUDA(cudaStreamSynchronize(ctx->stream));
         if (ctx->io) cudaFree(ctx->io);
         ctx->io = nullptr;
@@ -82,7 +100,6 @@ int ctx_io(qlc_ctx *ctx, size_t bytes, void **out) {
         QLC_CUDA(cudaMalloc(&ctx->io, want));
         ctx->io_bytes = want;
     }
-    *out = ctx->io;
     return QLC_OK;
 }
 
@@ -125,6 +142,7 @@ struct DevBuf {
 };
 
 int sync_and_check(qlc_ctx *ctx) {
+    QLC_TRY(fused_quiesce(ctx));
     QLC_CUDA(cudaStreamSynchronize(ctx->stream));
     DeviceStatus s;
     QLC_CUDA(cudaMemcpy(&s, ctx->d_status, sizeof(s), cudaMemcpyDeviceToHost));
@@ -252,8 +270,10 @@ int qlc_ctx_create(int device, qlc_ctx **out) {
     QLC_CUDA(cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming));
     QLC_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     QLC_CUDA(cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
-    QLC_CUDA(cudaEventCreateWithFlags(&ctx->ev_a, cudaEventDisableTiming));
-    QLC_CUDA(cudaEventCreateWithFlags(&ctx->ev_b, cudaEventDisableTiming));
+    for (int p = 0; p < 2; ++p) {
+        QLC_CUDA(cudaEventCreateWithFlags(&ctx->ev_in_free[p], cudaEventDisableTiming));
+        QLC_CUDA(cudaEventCreateWithFlags(&ctx->ev_out_free[p], cudaEventDisableTiming));
+    }
     QLC_CUDA(cudaMalloc(&ctx->d_status, sizeof(DeviceStatus)));
     QLC_CUDA(cudaMemset(ctx->d_status, 0, sizeof(DeviceStatus)));
     *out = ctx;
@@ -276,8 +296,10 @@ int qlc_ctx_destroy(qlc_ctx *ctx) {
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->pin) cudaFreeHost(ctx->pin);
     if (ctx->d_status) cudaFree(ctx->d_status);
-    cudaEventDestroy(ctx->ev_a);
-    cudaEventDestroy(ctx->ev_b);
+    for (int p = 0; p < 2; ++p) {
+        cudaEventDestroy(ctx->ev_in_free[p]);
+        cudaEventDestroy(ctx->ev_out_free[p]);
+    }
     cudaStreamDestroy(ctx->stream);
     cudaStreamDestroy(ctx->copy_stream);
     cudaStreamSynchronize(ctx->d2h_stream);
@@ -991,10 +1013,14 @@ static const size_t kSlabRows = getenv("QLC_SLAB_ROWS") ? (size_t)atoi(getenv("Q
 // The first copy in and the last copy out have nothing to overlap with, so the slabs ramp up and down: a quarter
 // and a half slab at either end, full slabs in between (8192 rows: 512, 1024, 2048, 2048, 1024, 1024, 512; a
 // third ramp step measured no better).
-static std::vector<size_t> slab_schedule(size_t batch) {
+// `streaming`: the caller keeps several submissions in flight, so the ends of one submission's copies overlap its
+// neighbours' and the ramp (shorter slabs at both ends, which shorten a lone call's exposed first copy in and last
+// copy out) would only add small, less efficient transfers.
+static std::vector<size_t> slab_schedule(size_t batch, bool streaming = false) {
     const size_t S = kSlabRows;
     std::vector<size_t> rows, ramp;
-    static const bool flat = getenv("QLC_FLAT_SLABS") != nullptr;  // diagnostics: equal slabs
+    static const bool flat_env = getenv("QLC_FLAT_SLABS") != nullptr;  // diagnostics: equal slabs
+    const bool flat = flat_env || streaming;
     size_t ramp_rows = 0;
     for (size_t r = S / 4; r && r < S; r *= 2) {
         ramp.push_back(r);
@@ -1123,8 +1149,32 @@ int qlc_qlora_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const voi
 
 // Queues forward + backward of one batch (host buffers) without waiting for any of it; *pipelined tells whether the
 // slab pipeline was used (false: the two synchronous calls ran and everything is already complete).
+// Diagnostics (QLC_HOST_PIPE_TIMING=1): device-side time stamps of every stage of the fused host pipeline, printed
+// four submissions later (by then they have completed; nothing waits for them).  One line per row slab.
+struct PipeTimeline {
+    std::vector<cudaEvent_t> ev;
+    size_t used = 0, slabs = 0;
+    uint64_t submission = 0;
+};
+static PipeTimeline g_pipe_tl[4];
+static cudaEvent_t g_pipe_base = nullptr;
+static uint64_t g_pipe_n = 0;
+constexpr size_t kPipeMarks = 8;  // per slab: h2d begin/end, compute begin, fwd end, bwd end, d2h begin, y out, dX out
+static void pipe_timeline_print(PipeTimeline &t) {
+    if (!t.used || cudaEventQuery(t.ev[t.used - 1]) != cudaSuccess) return;
+    fprintf(stderr, "[qlc host pipe] submission %llu, ms since the first one: slab | h2d begin, end | compute begin, fwd end, bwd end | d2h begin, Y out, dX out\n",
+            (unsigned long long)t.submission);
+    for (size_t c = 0; c < t.slabs; ++c) {
+        float ms[kPipeMarks];
+        for (size_t k = 0; k < kPipeMarks; ++k) cudaEventElapsedTime(&ms[k], g_pipe_base, t.ev[c * kPipeMarks + k]);
+        fprintf(stderr, "[qlc host pipe]   %2zu | %8.3f %8.3f | %8.3f %8.3f %8.3f | %8.3f %8.3f %8.3f\n", c, ms[0], ms[1], ms[2], ms[3],
+                ms[4], ms[5], ms[6], ms[7]);
+    }
+    t.used = 0;
+}
+
 static int fused_submit(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype, size_t batch, void *y,
-                        void *grad_x, float *grad_a, float *grad_b, bool *pipelined) {
+                        void *grad_x, float *grad_a, float *grad_b, bool streaming, bool *pipelined) {
     *pipelined = false;
     if (!ctx || !L) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
     QLC_TRY(same_device(ctx, L));
@@ -1142,25 +1192,45 @@ static int fused_submit(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *d
         return qlc_qlora_backward_host(ctx, L, x, dy, dtype, batch, grad_x, grad_a, grad_b);
     }
     *pipelined = true;
-    void *io = nullptr;
-    QLC_TRY(ctx_io(ctx, 2 * a256(nx * es) + 2 * a256(ny * es), &io));
-    char *dx = static_cast<char *>(io), *ddy = dx + a256(nx * es), *dyo = ddy + a256(ny * es), *dgx = dyo + a256(ny * es);
-    float *d_ga = L->r ? L->d_grad_bucket : nullptr;
-    float *d_gb = L->r ? L->d_grad_bucket + na : nullptr;
-    // Ordering against what is already queued, without stopping the host:
-    //  * the staged inputs (dx, ddy) are read by the compute of the previous submission: this one's copies in wait
-    //    for the end of that compute (ev_a), not for its copies out - the inbound link keeps working while the
-    //    previous submission's last results are still going out;
-    //  * the staged outputs (dyo, dgx) are read by the previous submission's copies out: the context's stream has
-    //    waited for those (ev_b) at the end of that submission, so this one's compute follows them in stream order.
-    if (!ctx->compute_done_recorded) {
-        QLC_CUDA(cudaEventRecord(ctx->ev_a, ctx->stream));
-        ctx->compute_done_recorded = true;
+    // Two sets of device staging buffers, used by consecutive submissions in turn: a submission's copies in never
+    // wait for the previous submission's compute, and its compute never waits for the previous submission's copies
+    // out - with two submissions in flight the host link stays busy in both directions without a gap.
+    const size_t g_bytes = a256((na + nb + 1) * 4);
+    const size_t set_bytes = 2 * a256(nx * es) + 2 * a256(ny * es) + g_bytes;
+    QLC_TRY(ctx_io_grow(ctx, 2 * set_bytes));
+    const int p = (int)(ctx->fused_submissions++ & 1);
+    char *dx = static_cast<char *>(ctx->io) + p * set_bytes, *ddy = dx + a256(nx * es), *dyo = ddy + a256(ny * es),
+         *dgx = dyo + a256(ny * es);
+    // Gradients wanted on the host are accumulated in this set's own bucket and leave on the copy-out stream; with
+    // grad_a == grad_b == NULL they go to the layer's bucket (qlc_layer_grad_bucket) and stay on the device.
+    const bool grads_out = L->r && (grad_a || grad_b);
+    float *g_stage = reinterpret_cast<float *>(dgx + a256(nx * es));
+    float *d_ga = L->r ? (grads_out ? g_stage : L->d_grad_bucket) : nullptr;
+    float *d_gb = L->r ? d_ga + na : nullptr;
+    QLC_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_in_free[p], 0));  // staged inputs of set p: read two submissions ago
+    QLC_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_out_free[p], 0));      // staged outputs of set p: copied out two submissions ago
+    const std::vector<size_t> sched = slab_schedule(batch, streaming);
+    static const bool timing = getenv("QLC_HOST_PIPE_TIMING") != nullptr;
+    PipeTimeline *tl = nullptr;
+    if (timing) {
+        tl = &g_pipe_tl[g_pipe_n % 4];
+        pipe_timeline_print(*tl);
+        if (!g_pipe_base) {
+            QLC_CUDA(cudaEventCreate(&g_pipe_base));
+            QLC_CUDA(cudaEventRecord(g_pipe_base, ctx->stream));
+        }
+        while (tl->ev.size() < sched.size() * kPipeMarks) {
+            cudaEvent_t e = nullptr;
+            QLC_CUDA(cudaEventCreate(&e));
+            tl->ev.push_back(e);
+        }
+        tl->slabs = sched.size();
+        tl->used = sched.size() * kPipeMarks;
+        tl->submission = g_pipe_n++;
     }
-    QLC_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_a, 0));
-    // One pipeline over row slabs: slab c's X and dY go in on the copy stream while slab c-1 computes (forward, then
-    // backward: X crosses the link once and serves both) and the Y and dX of slab c-2 go out on the third stream.
-    const std::vector<size_t> sched = slab_schedule(batch);
+    auto mark = [&](size_t c, size_t k, cudaStream_t st) {
+        if (tl) cudaEventRecord(tl->ev[c * kPipeMarks + k], st);
+    };
     size_t r0 = 0;
     for (size_t c = 0; c < sched.size(); r0 += sched[c], ++c) {
         const size_t rows = sched[c];
@@ -1169,37 +1239,46 @@ static int fused_submit(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *d
         QLC_TRY(chunk_event(ctx, 3 * c, &in_done));
         QLC_TRY(chunk_event(ctx, 3 * c + 1, &y_ready));
         QLC_TRY(chunk_event(ctx, 3 * c + 2, &gx_ready));
+        mark(c, 0, ctx->copy_stream);
         QLC_CUDA(cudaMemcpyAsync(dx + ox, static_cast<const char *>(x) + ox, rows * L->in_dim * es, cudaMemcpyHostToDevice,
                                  ctx->copy_stream));
         QLC_CUDA(cudaMemcpyAsync(ddy + oy, static_cast<const char *>(dy) + oy, rows * L->out_dim * es, cudaMemcpyHostToDevice,
                                  ctx->copy_stream));
         QLC_CUDA(cudaEventRecord(in_done, ctx->copy_stream));
+        mark(c, 1, ctx->copy_stream);
         QLC_CUDA(cudaStreamWaitEvent(ctx->stream, in_done, 0));
+        mark(c, 2, ctx->stream);
         QLC_TRY(umma_qlora_forward(ctx, L, dx + ox, rows, dyo + oy, dtype));
         QLC_CUDA(cudaEventRecord(y_ready, ctx->stream));
+        mark(c, 3, ctx->stream);
         QLC_TRY(umma_qlora_backward(ctx, L, reinterpret_cast<const __nv_bfloat16 *>(dx + ox),
                                     reinterpret_cast<const __nv_bfloat16 *>(ddy + oy), rows, dgx + ox, dtype, d_ga, d_gb,
                                     c > 0 ? 1 : 0));
         QLC_CUDA(cudaEventRecord(gx_ready, ctx->stream));
+        mark(c, 4, ctx->stream);
         QLC_CUDA(cudaStreamWaitEvent(ctx->d2h_stream, y_ready, 0));
+        mark(c, 5, ctx->d2h_stream);
         QLC_CUDA(cudaMemcpyAsync(static_cast<char *>(y) + oy, dyo + oy, rows * L->out_dim * es, cudaMemcpyDeviceToHost,
                                  ctx->d2h_stream));
+        mark(c, 6, ctx->d2h_stream);
         QLC_CUDA(cudaStreamWaitEvent(ctx->d2h_stream, gx_ready, 0));
         QLC_CUDA(cudaMemcpyAsync(static_cast<char *>(grad_x) + ox, dgx + ox, rows * L->in_dim * es, cudaMemcpyDeviceToHost,
                                  ctx->d2h_stream));
+        mark(c, 7, ctx->d2h_stream);
     }
-    if (L->r && grad_a && na) QLC_CUDA(cudaMemcpyAsync(grad_a, d_ga, na * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (L->r && grad_b && nb) QLC_CUDA(cudaMemcpyAsync(grad_b, d_gb, nb * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    QLC_CUDA(cudaEventRecord(ctx->ev_a, ctx->stream));  // end of this submission's compute
-    QLC_CUDA(cudaEventRecord(ctx->ev_b, ctx->d2h_stream));
-    QLC_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_b, 0));  // the context's stream now covers the copies out as well
+    QLC_CUDA(cudaEventRecord(ctx->ev_in_free[p], ctx->stream));  // end of this submission's compute
+    // (the copy-out stream has waited for the last slab's backward pass, which ends with the gradient contractions)
+    if (grads_out && grad_a && na) QLC_CUDA(cudaMemcpyAsync(grad_a, d_ga, na * 4, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    if (grads_out && grad_b && nb) QLC_CUDA(cudaMemcpyAsync(grad_b, d_gb, nb * 4, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    QLC_CUDA(cudaEventRecord(ctx->ev_out_free[p], ctx->d2h_stream));  // end of this submission
+    ctx->fused_open = true;
     return QLC_OK;
 }
 
 int qlc_qlora_forward_backward_host(qlc_ctx *ctx, qlc_layer *L, const void *x, const void *dy, int dtype, size_t batch,
                                     void *y, void *grad_x, float *grad_a, float *grad_b) {
     bool pipelined = false;
-    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, &pipelined));
+    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, false, &pipelined));
     return pipelined ? sync_and_check(ctx) : QLC_OK;
 }
 
@@ -1208,11 +1287,12 @@ int qlc_qlora_forward_backward_host_async(qlc_ctx *ctx, qlc_layer *L, const void
                                           uint64_t *ticket) {
     if (!ticket) return fail(QLC_ERR_INVALID_CONFIG, "null ticket");
     bool pipelined = false;
-    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, &pipelined));
+    QLC_TRY(fused_submit(ctx, L, x, dy, dtype, batch, y, grad_x, grad_a, grad_b, true, &pipelined));
     const uint64_t t = ctx->tickets_issued;
     cudaEvent_t &ev = ctx->ticket_ev[t % qlc_ctx::kTickets];
     if (!ev) QLC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-    QLC_CUDA(cudaEventRecord(ev, ctx->stream));
+    // the copy-out stream ends a pipelined submission (it has waited for all of its compute)
+    QLC_CUDA(cudaEventRecord(ev, pipelined ? ctx->d2h_stream : ctx->stream));
     ctx->tickets_issued = t + 1;
     *ticket = t;
     return QLC_OK;

@@ -63,9 +63,12 @@ struct qlc_ctx {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaStream_t d2h_stream = nullptr;   // device-to-host copies of the pipelined *_host entry points
     std::vector<cudaEvent_t> chunk_events;  // reused by the pipelined *_host entry points
-    // asynchronous host-buffer calls: end of a submission's compute / of its device-to-host copies
-    cudaEvent_t ev_a = nullptr, ev_b = nullptr;
-    bool compute_done_recorded = false;
+    // Asynchronous host-buffer calls (forward + backward of one batch): consecutive submissions alternate between
+    // two sets of device staging buffers.  ev_in_free[p]: the compute of the last submission that used set p has
+    // ended (its staged inputs may be overwritten); ev_out_free[p]: that submission's copies out have ended.
+    cudaEvent_t ev_in_free[2] = {nullptr, nullptr}, ev_out_free[2] = {nullptr, nullptr};
+    uint64_t fused_submissions = 0;
+    bool fused_open = false;  // copies of such submissions may still run on the copy streams
     // completion tickets of the asynchronous host-buffer calls: a ring of events, ticket t -> ticket_ev[t % 8]
     static constexpr int kTickets = 8;
     cudaEvent_t ticket_ev[kTickets] = {nullptr};
