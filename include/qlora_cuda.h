@@ -280,7 +280,11 @@ int qlc_qlora_forward_dev_noalloc(qlc_ctx *ctx, qlc_layer *layer, const void *d_
 /* ---- paged 8-bit Adam --------------------------------------------------------------- */
 
 /* AdamConfig (qlora-core/src/optim.rs:33-58).  max_resident_pages == SIZE_MAX keeps every
- * state page on the device (the reference default, usize::MAX). */
+ * state page on the device (the reference default, usize::MAX).  An optimiser that holds more pages than
+ * max_resident_pages keeps ALL of its state in pinned host memory; the step kernel then reads and writes the
+ * pages in place over the host link (nothing of the state is resident on the device), or, with the environment
+ * variable QLC_ADAM_PAGED_MODE=slots (hybrid), copies them through min(max_resident_pages, 8) device slots in both
+ * directions (on the way in only).  Results are bit-identical in every mode. */
 typedef struct qlc_adam_config {
     float lr;
     float beta1;
