@@ -85,6 +85,12 @@ int qlc_ctx_create(int device, qlc_ctx **out);
  * stream and scratch memory are released when the last of them is destroyed. */
 int qlc_ctx_destroy(qlc_ctx *ctx);
 int qlc_ctx_set_precision(qlc_ctx *ctx, int precision);
+/* The weight GEMMs run as ONE wave of CTA pairs, one pair per two SMs, each pair walking its share of the tiles.
+ * A kernel of another stream that holds an SM when such a GEMM starts (a collective of the gradient exchange,
+ * for instance) keeps one pair from starting until it ends, and that pair's tiles wait with it.  A host that
+ * overlaps such kernels with the layer passes reserves their SMs here: the GEMMs then use (SMs - sms) / 2 pairs.
+ * sms is rounded down to an even number; 0 (the default) uses every SM.  No counterpart in the reference. */
+int qlc_ctx_set_reserved_sms(qlc_ctx *ctx, int sms);
 /* Blocks until everything enqueued on the context's stream has finished, then reports any
  * device-side status raised by the kernels (e.g. a bounded wait that gave up). */
 int qlc_ctx_synchronize(qlc_ctx *ctx);

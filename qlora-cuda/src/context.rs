@@ -76,6 +76,11 @@ impl GpuContext {
         check(unsafe { ffi::qlc_ctx_set_precision(self.raw, code) })
     }
 
+    /// SMs the one-wave weight GEMMs leave free for kernels of other streams (a collective that overlaps them).
+    pub fn set_reserved_sms(&self, sms: i32) -> Result<(), QloraError> {
+        check(unsafe { ffi::qlc_ctx_set_reserved_sms(self.raw, sms) })
+    }
+
     /// Waits for everything queued on the context's stream and reports a status raised by a kernel.
     pub fn synchronize(&self) -> Result<(), QloraError> {
         check(unsafe { ffi::qlc_ctx_synchronize(self.raw) })

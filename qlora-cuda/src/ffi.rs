@@ -59,6 +59,7 @@ extern "C" {
     pub fn qlc_ctx_create(device: c_int, out: *mut *mut qlc_ctx) -> c_int;
     pub fn qlc_ctx_destroy(ctx: *mut qlc_ctx) -> c_int;
     pub fn qlc_ctx_set_precision(ctx: *mut qlc_ctx, precision: c_int) -> c_int;
+    pub fn qlc_ctx_set_reserved_sms(ctx: *mut qlc_ctx, sms: c_int) -> c_int;
     pub fn qlc_ctx_synchronize(ctx: *mut qlc_ctx) -> c_int;
     pub fn qlc_ctx_stream(ctx: *mut qlc_ctx) -> *mut c_void;
 

@@ -75,6 +75,10 @@ class GpuContext:
     def set_precision(self, precision: int) -> None:
         check(lib.qlc_ctx_set_precision(self._h, precision))
 
+    def set_reserved_sms(self, sms: int) -> None:
+        """SMs the one-wave weight GEMMs leave free for kernels of other streams (a collective that overlaps them)."""
+        check(lib.qlc_ctx_set_reserved_sms(self._h, int(sms)))
+
     def synchronize(self) -> None:
         check(lib.qlc_ctx_synchronize(self._h))
 

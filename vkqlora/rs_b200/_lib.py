@@ -47,6 +47,7 @@ SIGNATURES = {
     "qlc_ctx_create": (_i, [_i, _pp]),
     "qlc_ctx_destroy": (_i, [_vp]),
     "qlc_ctx_set_precision": (_i, [_vp, _i]),
+    "qlc_ctx_set_reserved_sms": (_i, [_vp, _i]),
     "qlc_ctx_synchronize": (_i, [_vp]),
     "qlc_ctx_stream": (_vp, [_vp]),
     "qlc_ctx_copy_to_host": (_i, [_vp, _vp, _vp, _sz]),

@@ -325,6 +325,14 @@ int qlc_ctx_set_precision(qlc_ctx *ctx, int precision) {
     return QLC_OK;
 }
 
+int qlc_ctx_set_reserved_sms(qlc_ctx *ctx, int sms) {
+    if (!ctx) return fail(QLC_ERR_INVALID_CONFIG, "null context");
+    if (sms < 0 || sms > ctx->sm_count / 2)
+        return fail(QLC_ERR_INVALID_CONFIG, "reserved SMs must be in [0, %d]", ctx->sm_count / 2);
+    ctx->reserved_sms = sms & ~1;  // whole pairs
+    return QLC_OK;
+}
+
 int qlc_ctx_synchronize(qlc_ctx *ctx) {
     if (!ctx) return fail(QLC_ERR_INVALID_CONFIG, "null context");
     QLC_CUDA(cudaSetDevice(ctx->device));

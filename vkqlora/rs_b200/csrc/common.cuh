@@ -75,6 +75,7 @@ struct qlc_ctx {
     uint64_t tickets_issued = 0;
     int precision = QLC_PRECISION_AUTO;
     int sm_count = 0;
+    int reserved_sms = 0;  // SMs the one-wave (persistent) kernels leave free for kernels of other streams (qlc_ctx_set_reserved_sms)
     uint64_t launches = 0;
     qlc::DeviceStatus *d_status = nullptr;  // device memory, read back by qlc_ctx_synchronize
     // Scratch arena for intermediates of the layer passes (T1, Ds, split partials, staged

@@ -1385,10 +1385,15 @@ int launch_gemm(qlc_ctx *ctx, int prof_slot, const CUtensorMap &tA, const CUtens
 // Cutting the tiles of the paired-CTA GEMM's last wave along the contraction: with S pairs resident at a
 // time, the `rest` tiles beyond the last full wave are each cut into `chunks` pieces when the pieces still fit
 // into one wave; the GPU then ends on a short full wave instead of a long, mostly idle one.
+// CTA pairs one launch of the persistent GEMM runs with: every pair of SMs, less the reserved ones.
+static uint32_t pair_slots(const qlc_ctx *ctx) {
+    const int sms = ctx->sm_count - ctx->reserved_sms;
+    return sms >= 2 ? (uint32_t)sms / 2 : 1u;
+}
 void kcut_plan(const qlc_ctx *ctx, size_t M, size_t N, size_t k_steps, uint32_t *rest, uint32_t *chunks) {
     static const bool no_cut = getenv("QLC_NO_KCUT") != nullptr;  // diagnostics
     const uint32_t tiles = (uint32_t)(ceil_div(M, 4 * kBM) * ceil_div(N, 256));
-    const uint32_t slots = (uint32_t)ctx->sm_count / 2;
+    const uint32_t slots = pair_slots(ctx);
     *rest = tiles % slots;
     uint32_t c = (*rest && !no_cut) ? slots / *rest : 1u;
     if (c > 4) c = 4;
@@ -1447,7 +1452,7 @@ int launch_gemm2(qlc_ctx *ctx, int prof_slot, const CUtensorMap &tA, const CUten
         // the persistent kernel's own sums: per leader CTA, cycles
         auto kern3 = umma_gemm3_kernel<B_MN, TF32, true>;
         QLC_CUDA(cudaFuncSetAttribute(kern3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem3));
-        const uint32_t pairs = items < (uint32_t)ctx->sm_count / 2 ? items : (uint32_t)ctx->sm_count / 2;
+        const uint32_t pairs = items < pair_slots(ctx) ? items : pair_slots(ctx);
         const size_t ctas = 2 * (size_t)pairs;
         long long *d = nullptr;
         QLC_CUDA(cudaMalloc(&d, ctas * 16 * sizeof(long long)));
@@ -1481,7 +1486,7 @@ int launch_gemm2(qlc_ctx *ctx, int prof_slot, const CUtensorMap &tA, const CUten
         if ((size_t)ctx->umma_smem_optin < kSmem3)
             return fail(QLC_ERR_GPU, "kernel needs %zu bytes of shared memory, device allows %d", kSmem3, ctx->umma_smem_optin);
         QLC_CUDA(cudaFuncSetAttribute(kern3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem3));
-        const uint32_t pairs = items < (uint32_t)ctx->sm_count / 2 ? items : (uint32_t)ctx->sm_count / 2;
+        const uint32_t pairs = items < pair_slots(ctx) ? items : pair_slots(ctx);
         prof_begin(ctx, prof_slot);
         QLC_CUDA(launch_pdl(kern3, dim3(2 * pairs), dim3(kThreads3), kSmem3, ctx->stream, tA, tAe, tBe, tOut, args));
         prof_end(ctx);
