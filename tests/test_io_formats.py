@@ -103,3 +103,51 @@ def test_quantize_from_checkpoint_dtype_is_bit_exact(io, oracle, tmp_path, store
     assert np.array_equal(q.codes(), ref.codes)
     assert np.array_equal(q.absmax_codes(), ref.absmax_codes)
     assert np.array_equal(q.absmax2().view(np.uint32), ref.absmax2.view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_persisted_nf4_payload_and_adam_state_round_trip(io, oracle, tmp_path):
+    """A quantised tensor saved with save_quantized_npz comes back bit for bit without a quantisation pass (double
+    quantised and plain-scale forms), and a saved optimiser state continues the trajectory bit for bit."""
+    import vkqlora.rs_b200 as v
+    ctx = v.GpuContext(0)
+    rows, cols = 96, 200
+    w = normal(11, rows * cols, 0.02)
+    qd = v.QuantizedTensor.quantize(w, rows, cols, v.QuantConfig(64, True), ctx)
+    qf = v.QuantizedTensor.quantize(w, rows, cols, v.QuantConfig(32, False), ctx)
+    p = str(tmp_path / "payload.npz")
+    io.save_quantized_npz(p, {"layers.0.q_proj": qd, "layers.0.v_proj": qf})
+    with zipfile.ZipFile(p) as z:
+        assert all(i.compress_type == zipfile.ZIP_STORED for i in z.infolist())
+    back = io.load_quantized_npz(p, ctx)
+    assert sorted(back) == ["layers.0.q_proj", "layers.0.v_proj"]
+    bd, bf = back["layers.0.q_proj"], back["layers.0.v_proj"]
+    assert bd.uses_double_quant() and not bf.uses_double_quant()
+    assert (bd.rows(), bd.cols(), bd.block_size()) == (rows, cols, 64) and bf.block_size() == 32
+    assert np.array_equal(bd.codes(), qd.codes()) and np.array_equal(bd.absmax_codes(), qd.absmax_codes())
+    assert np.array_equal(bd.absmax2().view(np.uint32), qd.absmax2().view(np.uint32))
+    assert np.array_equal(bd.dequantize().view(np.uint32), qd.dequantize().view(np.uint32))
+    assert np.array_equal(bf.codes(), qf.codes())
+    assert np.array_equal(bf.dequantize().view(np.uint32), qf.dequantize().view(np.uint32))
+    ref = oracle.quantize_nf4(w, rows, cols)
+    assert np.array_equal(bd.dequantize().view(np.uint32), ref.dequantize().view(np.uint32))
+
+    sizes = [1000, 4096 + 13]
+    a = v.Adam8bit(v.AdamConfig(), ctx)
+    pa = [normal(30 + i, n, 0.01) for i, n in enumerate(sizes)]
+    for t in range(2):
+        a.step(pa, [normal(500 * t + i, n, 0.01) for i, n in enumerate(sizes)])
+    ps = str(tmp_path / "adam.npz")
+    io.save_adam_state_npz(ps, a, len(sizes))
+    b = v.Adam8bit(v.AdamConfig(max_resident_pages=1), ctx)  # restored into a paged optimiser
+    assert io.load_adam_state_npz(ps, b) == len(sizes)
+    pb = [x.copy() for x in pa]
+    g = [normal(900 + i, n, 0.01) for i, n in enumerate(sizes)]
+    a.step(pa, g)
+    b.step(pb, g)
+    for i in range(len(sizes)):
+        assert np.array_equal(pa[i].view(np.uint32), pb[i].view(np.uint32))
+        sa, sb = a.get_state(i), b.get_state(i)
+        assert sa["step"] == sb["step"] == 3
+        for k in ("m_codes", "v_codes", "m_scales", "v_scales"):
+            assert np.array_equal(sa[k], sb[k]), (i, k)

@@ -146,3 +146,68 @@ def save_adapters_npz(path: str, adapters: Mapping[str, np.ndarray]) -> None:
 def load_adapters_npz(path: str) -> Dict[str, np.ndarray]:
     with np.load(path) as z:
         return {k: np.ascontiguousarray(z[k], dtype=np.float32) for k in z.files}
+
+
+# ---- persisted NF4 payloads and optimiser state -------------------------------------------------------------
+# The reference has no on-disk form for either (it re-quantises the checkpoint at every start and keeps the
+# optimiser state in memory only).  Both are stored `.npz` files of plain arrays, so any numpy can read them.
+
+def save_quantized_npz(path: str, tensors: Mapping[str, QuantizedTensor]) -> None:
+    """NF4 payloads as they live on the device: per tensor `<name>.shape` = (rows, cols, block_size), `<name>.codes`
+    (packed nibbles, quant.rs:132-136) and either `<name>.absmax_codes` + `<name>.absmax2` (double quantisation,
+    quant.rs:283-299) or `<name>.scales` (fp32 block scales).  4.127 bit per weight at block 64."""
+    out = {}
+    for name, q in tensors.items():
+        out[f"{name}.shape"] = np.asarray([q.rows(), q.cols(), q.block_size()], dtype="<i8")
+        out[f"{name}.codes"] = q.codes()
+        if q.uses_double_quant():
+            out[f"{name}.absmax_codes"] = q.absmax_codes()
+            out[f"{name}.absmax2"] = np.ascontiguousarray(q.absmax2(), dtype="<f4")
+        else:
+            out[f"{name}.scales"] = np.ascontiguousarray(q.block_scales(), dtype="<f4")
+    np.savez(path, **out)
+
+
+def load_quantized_npz(path: str, ctx: Optional[GpuContext] = None) -> Dict[str, QuantizedTensor]:
+    """The inverse of save_quantized_npz: the tensors come back bit for bit (codes, 8-bit scales, second-level
+    absmax), without a quantisation pass."""
+    ctx = ctx or default_context()
+    res: Dict[str, QuantizedTensor] = {}
+    with np.load(path) as z:
+        names = sorted({k[: -len(".shape")] for k in z.files if k.endswith(".shape")})
+        for name in names:
+            rows, cols, block = (int(v) for v in z[f"{name}.shape"])
+            if f"{name}.absmax_codes" in z.files:
+                res[name] = QuantizedTensor.from_double_quant_parts(rows, cols, block, z[f"{name}.codes"],
+                                                                    z[f"{name}.absmax_codes"], z[f"{name}.absmax2"], ctx)
+            elif f"{name}.scales" in z.files:
+                res[name] = QuantizedTensor.from_raw_parts(rows, cols, block, z[f"{name}.codes"], z[f"{name}.scales"], ctx)
+            else:
+                raise InvalidConfig(2, f"invalid config: {name} has neither absmax_codes nor scales in {path}")
+    return res
+
+
+def save_adam_state_npz(path: str, opt, n_tensors: int) -> None:
+    """The 8-bit state of the first `n_tensors` parameter tensors of an Adam8bit (ParamState, optim.rs:104-112:
+    m / v codes, their block scales, the step count), resident or paged."""
+    out = {"n_tensors": np.asarray([n_tensors], dtype="<i8")}
+    for i in range(n_tensors):
+        st = opt.get_state(i)
+        out[f"{i}.meta"] = np.asarray([st["numel"], st["step"]], dtype="<i8")
+        for k in ("m_codes", "v_codes"):
+            out[f"{i}.{k}"] = st[k]
+        for k in ("m_scales", "v_scales"):
+            out[f"{i}.{k}"] = np.ascontiguousarray(st[k], dtype="<f4")
+    np.savez(path, **out)
+
+
+def load_adam_state_npz(path: str, opt) -> int:
+    """Restores save_adam_state_npz's states into `opt` in order (an optimiser built with the same block size);
+    the next step continues the saved trajectory bit for bit.  Returns the number of tensors restored."""
+    with np.load(path) as z:
+        n = int(z["n_tensors"][0])
+        for i in range(n):
+            numel, step = (int(v) for v in z[f"{i}.meta"])
+            opt.set_state(i, dict(numel=numel, step=step, m_codes=z[f"{i}.m_codes"], v_codes=z[f"{i}.v_codes"],
+                                  m_scales=z[f"{i}.m_scales"], v_scales=z[f"{i}.v_scales"]))
+    return n
