@@ -36,6 +36,8 @@ METRIC, UNIT = "qlora_linear_fwd_bwd_tokens_per_s", "tokens/s"
 GEMM_DRAM_TRAFFIC_PER_LAUNCH = 121.9e6
 # SMs left to the NCCL kernels of the gradient exchange at N > 1 (NCCL_MAX_CTAS=2: two CTAs, possibly on two TPCs)
 RESERVED_SMS = int(os.environ.get("QLC_BENCH_RESERVED_SMS", "4"))
+# end-to-end leg: submissions kept in flight (each on its own set of pinned host buffers)
+E2E_DEPTH = max(2, int(os.environ.get("QLC_BENCH_E2E_DEPTH", "2")))
 
 
 def base_config(world):
@@ -449,12 +451,13 @@ def ours_arm(args, dist_):
             hs["dy"].copy_(dy.reshape(-1).cpu())
             return hs
 
-        sets = [host_set(), host_set()]
+        depth = E2E_DEPTH
+        sets = [host_set() for _ in range(depth)]
         bucket_ptr, _n = layer.grad_bucket()
-        tickets = [None, None]
+        tickets = [None] * depth
         reduced = torch.cuda.Event()
         stepped = torch.cuda.Event()
-        g_done = [torch.cuda.Event(), torch.cuda.Event()]
+        g_done = [torch.cuda.Event() for _ in range(depth)]
         e2e_count = [0]
 
         def e2e_wait(k):
@@ -465,7 +468,7 @@ def ours_arm(args, dist_):
                 tickets[k] = None
 
         def e2e_step():
-            k = e2e_count[0] & 1
+            k = e2e_count[0] % depth
             e2e_count[0] += 1
             e2e_wait(k)  # this buffer set's previous step has delivered: its results would be consumed here
             hs = sets[k]
@@ -491,8 +494,8 @@ def ours_arm(args, dist_):
                 g_done[k].record(cext)
 
         def e2e_drain():
-            e2e_wait(0)
-            e2e_wait(1)
+            for k in range(depth):
+                e2e_wait(k)
             ctx.synchronize()
             if world > 1:
                 cctx.synchronize()
