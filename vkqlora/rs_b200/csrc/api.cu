@@ -287,6 +287,7 @@ int qlc_ctx_destroy(qlc_ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamSynchronize(ctx->d2h_stream);  // copies out of asynchronous host-buffer submissions read the staging area
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->io) cudaFree(ctx->io);
     for (auto &pe : ctx->prof_pending) {
