@@ -292,3 +292,36 @@ def test_batch_shape_can_change_between_calls(v):
         for (li, kind), (ga, gb) in want_grads.items():
             a, b = m.adapter_grads(li, kind, rank)
             assert rel_fro(a, ga) <= 5e-2 and rel_fro(b, gb) <= 5e-2, (n_seq, seq_len, kind, rel_fro(a, ga), rel_fro(b, gb))
+
+
+@pytest.mark.gpu
+def test_merged_gate_up_layer_equals_the_two_layers(v):
+    """MLP width 256 at hidden 128: gate holds 32 768 = 2 x 16 384 elements, so the NF4 payload of gate and up one
+    after the other is the payload of the (2I, h) matrix and the bf16 pipeline runs them as ONE layer (one forward
+    GEMM, one input-gradient GEMM over both contractions).  A second model with the same weights gets an adapter
+    with B = 0 on `up`, which keeps gate and up as two layers: its logits must be bit-identical (every output
+    element accumulates the same products in the same order) and its q / v gradients agree to the bf16 rounding of
+    the two input gradients that the merged layer no longer rounds separately.  Both also match the oracle."""
+    kw = dict(hidden=128, layers=2, heads=2, kv_heads=1, intermediate=256, vocab=128)
+    rank, alpha, n_seq, seq_len = 8, 16.0, 2, 150
+    rng = np.random.default_rng(12)
+    ids = rng.integers(0, kw["vocab"], n_seq * seq_len)
+    dlogits = (rng.standard_normal((n_seq * seq_len, kw["vocab"])) * 0.1).astype(np.float32)
+    ctx = v.GpuContext(0)
+    ctx.set_precision(v.PRECISION_BF16)
+    merged, ref, cfg = _build(v, ctx, kw, seed=47, rank=rank, alpha=alpha)
+    separate, _, _ = _build(v, ctx, kw, seed=47, rank=rank, alpha=alpha)
+    for li in range(cfg.layers):
+        a = (rng.standard_normal((4, kw["hidden"])) * 0.1).astype(np.float32)
+        separate.attach_adapter(li, "up", a, np.zeros((kw["intermediate"], 4), np.float32), 4, 8.0)
+    want_logits, want_grads = _oracle_batch(ref, ids, n_seq, seq_len, dlogits)
+    got_m, got_s = merged.forward(ids, n_seq, seq_len), separate.forward(ids, n_seq, seq_len)
+    assert np.array_equal(got_m, got_s)
+    assert rel_fro(got_m, want_logits) <= 2e-2
+    merged.backward(ids, dlogits, n_seq, seq_len)
+    separate.backward(ids, dlogits, n_seq, seq_len)
+    for (li, kind), (ga, gb) in want_grads.items():
+        am, bm = merged.adapter_grads(li, kind, rank)
+        as_, bs = separate.adapter_grads(li, kind, rank)
+        assert rel_fro(am, as_) <= 1e-2 and rel_fro(bm, bs) <= 1e-2, (li, kind, rel_fro(am, as_), rel_fro(bm, bs))
+        assert rel_fro(am, ga) <= 5e-2 and rel_fro(bm, gb) <= 5e-2, (li, kind, rel_fro(am, ga), rel_fro(bm, gb))

@@ -156,6 +156,8 @@ int sync_and_check(qlc_ctx *ctx) {
 
 bool mul_overflows(size_t a, size_t b, size_t *out) { return __builtin_mul_overflow(a, b, out); }
 
+}  // namespace
+
 int alloc_qtensor(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, bool dq, qlc_qtensor **out) {
     qlc_qtensor *q = new (std::nothrow) qlc_qtensor();
     if (!q) return fail(QLC_ERR_GPU, "out of host memory");
@@ -189,6 +191,8 @@ int alloc_qtensor(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, boo
     *out = q;
     return QLC_OK;
 }
+
+namespace {
 
 void qtensor_retain(qlc_qtensor *q) { q->refs += 1; }
 

@@ -146,6 +146,7 @@ namespace qlc {
 // ---- launchers implemented in the .cu files -------------------------------------------------
 // quant_kernels.cu
 int launch_quantize_nf4(qlc_ctx *ctx, const float *d_w, qlc_qtensor *q);
+int alloc_qtensor(qlc_ctx *ctx, size_t rows, size_t cols, size_t block_size, bool dq, qlc_qtensor **out);  // empty payload
 int launch_dequantize(qlc_ctx *ctx, const qlc_qtensor *q, void *d_out, int dtype);
 int launch_decode_block_scales(qlc_ctx *ctx, const qlc_qtensor *q, float *d_out);
 int launch_refresh_adapters(qlc_ctx *ctx, qlc_layer *const *layers, size_t n);

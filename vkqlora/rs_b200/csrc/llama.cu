@@ -169,9 +169,11 @@ __global__ void pipe_norm_bwd_kernel(const float2 *__restrict__ x, const float2 
     const size_t at = row * h2;
     auto dy_at = [&](int j) {
         float2 d = __bfloat1622float2(dy1[at + j]);
-        const float2 e = __bfloat1622float2(dy2[at + j]);
-        d.x += e.x;
-        d.y += e.y;
+        if (dy2) {
+            const float2 e = __bfloat1622float2(dy2[at + j]);
+            d.x += e.x;
+            d.y += e.y;
+        }
         if (dy3) {
             const float2 f = __bfloat1622float2(dy3[at + j]);
             d.x += f.x;
@@ -380,29 +382,33 @@ __global__ void attn_bwd_finish_kernel(const float *__restrict__ dqr, const floa
     *reinterpret_cast<uint4 *>(y + at + kHeadDim / 2) = pack8(hi);
 }
 
+// gate / up (and dg / du below) are read with a row stride of ld8 16-byte words, cols8 words per row: two (T, I)
+// matrices (ld8 == cols8) or the two halves of one (T, 2I) matrix (ld8 == 2 * cols8); act and d_act are (T, I).
 __global__ void swiglu_fwd_bf16_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up, uint4 *__restrict__ act,
-                                       size_t n8) {
+                                       size_t n8, uint32_t cols8, uint32_t ld8) {
     pdl_trigger();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n8) return;
+    const size_t row = i / cols8, at = row * ld8 + (i - row * cols8);
     float g[8], u[8], a[8];
-    unpack8(gate[i], g);
-    unpack8(up[i], u);
+    unpack8(gate[at], g);
+    unpack8(up[at], u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = g[e] / (1.0f + __expf(-g[e])) * u[e];
     act[i] = pack8(a);
 }
 __global__ void swiglu_bwd_bf16_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
                                        const uint4 *__restrict__ d_act, uint4 *__restrict__ dg, uint4 *__restrict__ du,
-                                       size_t n8) {
+                                       size_t n8, uint32_t cols8, uint32_t ld8) {
     pdl_trigger();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n8) return;
+    const size_t row = i / cols8, at = row * ld8 + (i - row * cols8);
     float g[8], u[8], d[8], og[8], ou[8];
-    unpack8(gate[i], g);
-    unpack8(up[i], u);
+    unpack8(gate[at], g);
+    unpack8(up[at], u);
     unpack8(d_act[i], d);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -410,8 +416,8 @@ __global__ void swiglu_bwd_bf16_kernel(const uint4 *__restrict__ gate, const uin
         og[e] = d[e] * u[e] * (sg * (1.0f + g[e] * (1.0f - sg)));
         ou[e] = d[e] * (g[e] * sg);
     }
-    dg[i] = pack8(og);
-    du[i] = pack8(ou);
+    dg[at] = pack8(og);
+    du[at] = pack8(ou);
 }
 // out may be one of the inputs (element i only depends on element i)
 __global__ void add_kernel(const float *a, const float *b, const float *c, float *out, size_t n) {
@@ -897,6 +903,10 @@ struct LlamaCache {  // per block, what the backward pass needs (llama.rs:471-48
 struct LlamaLayer {
     float *attn_norm = nullptr, *mlp_norm = nullptr;
     qlc_layer *proj[QLC_LLAMA_PROJ_COUNT] = {nullptr};
+    // gate and up as ONE layer with 2 * intermediate output features (its NF4 payload is the two payloads one after
+    // the other), built when that concatenation equals quantising the two matrices separately; the bf16 pipeline
+    // then runs one forward GEMM and one input-gradient GEMM (contraction over both) instead of two each
+    qlc_layer *gate_up = nullptr;
     LlamaCache c;
 };
 struct qlc_llama {
@@ -1005,8 +1015,11 @@ int ensure_capacity(qlc_llama *m, size_t n_seq, size_t seq_len) {
             for (__nv_bfloat16 **p : hb) QLC_TRY(dev_alloc_t(m, p, T * h));
             QLC_TRY(dev_alloc_t(m, &k.kr_b, T * kv));
             QLC_TRY(dev_alloc_t(m, &k.v_b, T * kv));
-            __nv_bfloat16 **ib[] = {&k.gate_b, &k.up_b, &k.act_b};
-            for (__nv_bfloat16 **p : ib) QLC_TRY(dev_alloc_t(m, p, T * I));
+            // gate and up share one allocation: two (T, I) matrices, or one (T, 2I) matrix when the block runs
+            // the merged gate_up layer
+            QLC_TRY(dev_alloc_t(m, &k.gate_b, 2 * T * I));
+            k.up_b = k.gate_b + T * I;
+            QLC_TRY(dev_alloc_t(m, &k.act_b, T * I));
             continue;
         }
         QLC_TRY(dev_alloc_t(m, &k.x_in, T * h));
@@ -1047,8 +1060,9 @@ int ensure_capacity(qlc_llama *m, size_t n_seq, size_t seq_len) {
         QLC_TRY(dev_alloc_t(m, &m->dv_b, T * kv));
         QLC_TRY(dev_alloc_t(m, &m->dk_parts, (c.heads / c.kv_heads) * T * kv));
         QLC_TRY(dev_alloc_t(m, &m->dv_parts, (c.heads / c.kv_heads) * T * kv));
-        __nv_bfloat16 **ib[] = {&m->d_act_b, &m->dg_b, &m->du_b};
-        for (__nv_bfloat16 **p : ib) QLC_TRY(dev_alloc_t(m, p, T * I));
+        QLC_TRY(dev_alloc_t(m, &m->d_act_b, T * I));
+        QLC_TRY(dev_alloc_t(m, &m->dg_b, 2 * T * I));  // dg and du: two (T, I) matrices or one (T, 2I) matrix
+        m->du_b = m->dg_b + T * I;
     } else {
         float **hs[] = {&m->dx, &m->dx2, &m->dxn, &m->dxn2, &m->dxn3, &m->d_attn, &m->dqr, &m->dq, &m->tmp_h, &m->q_tmp};
         for (float **p : hs) QLC_TRY(dev_alloc_t(m, p, T * h));
@@ -1171,6 +1185,13 @@ int lanes_join(qlc_llama *m, int n) {
     }
     return QLC_OK;
 }
+// The merged gate_up layer stands in for gate and up while neither of them has an adapter.
+bool uses_gate_up(const LlamaLayer &L) {
+    static const bool off = getenv("QLC_LLAMA_NO_GATE_UP") != nullptr;  // diagnostics
+    return !off && L.gate_up && L.proj[QLC_LLAMA_GATE] && L.proj[QLC_LLAMA_UP] && L.proj[QLC_LLAMA_GATE]->r == 0 &&
+           L.proj[QLC_LLAMA_UP]->r == 0;
+}
+
 int pipe_fwd(qlc_llama *m, int lane, qlc_layer *L, const __nv_bfloat16 *x, size_t T, void *y, int y_dtype) {
     return umma_qlora_forward(lane_ctx(m, lane), L, x, T, y, y_dtype, false);
 }
@@ -1223,12 +1244,20 @@ int run_forward_pipeline(qlc_llama *m, size_t n_seq, size_t seq_len) {
         // x_mid = x_in + attention branch, and its normalised copy for the MLP, in one pass
         LK(pipe_norm_fwd_kernel, rows_grid, 256, cf2(k.x_in), cb2(m->tmp_b), f2(k.x_mid), cf2(L.mlp_norm), c.rms_eps, no_f32x2,
            b2(k.xn_mlp_b), T, h2);
-        QLC_TRY(lanes_fork(m, 1));
-        QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_GATE], k.xn_mlp_b, T, k.gate_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_fwd(m, 1, L.proj[QLC_LLAMA_UP], k.xn_mlp_b, T, k.up_b, QLC_DTYPE_BF16));
-        QLC_TRY(lanes_join(m, 1));
-        LK(swiglu_fwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
-           reinterpret_cast<const uint4 *>(k.up_b), reinterpret_cast<uint4 *>(k.act_b), T * I / 8);
+        if (uses_gate_up(L)) {
+            QLC_TRY(pipe_fwd(m, 0, L.gate_up, k.xn_mlp_b, T, k.gate_b, QLC_DTYPE_BF16));  // (T, 2I): gate | up
+            LK(swiglu_fwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
+               reinterpret_cast<const uint4 *>(k.gate_b + I), reinterpret_cast<uint4 *>(k.act_b), T * I / 8, (uint32_t)(I / 8),
+               (uint32_t)(2 * I / 8));
+        } else {
+            QLC_TRY(lanes_fork(m, 1));
+            QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_GATE], k.xn_mlp_b, T, k.gate_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_fwd(m, 1, L.proj[QLC_LLAMA_UP], k.xn_mlp_b, T, k.up_b, QLC_DTYPE_BF16));
+            QLC_TRY(lanes_join(m, 1));
+            LK(swiglu_fwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
+               reinterpret_cast<const uint4 *>(k.up_b), reinterpret_cast<uint4 *>(k.act_b), T * I / 8, (uint32_t)(I / 8),
+               (uint32_t)(I / 8));
+        }
         QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_DOWN], k.act_b, T, m->tmp_b, QLC_DTYPE_BF16));
         // x_out = x_mid + MLP branch, normalised for the next block's attention (or by the final norm)
         if (last)
@@ -1265,16 +1294,29 @@ int run_backward_pipeline(qlc_llama *m, size_t n_seq, size_t seq_len, bool dlogi
         LlamaCache &k = L.c;
         // MLP branch (llama.rs:554-575)
         QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_DOWN], k.act_b, dx_b, T, m->d_act_b, QLC_DTYPE_BF16));
-        LK(swiglu_bwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
-           reinterpret_cast<const uint4 *>(k.up_b), reinterpret_cast<const uint4 *>(m->d_act_b),
-           reinterpret_cast<uint4 *>(m->dg_b), reinterpret_cast<uint4 *>(m->du_b), T * I / 8);
-        QLC_TRY(lanes_fork(m, 1));
-        QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_GATE], k.xn_mlp_b, m->dg_b, T, m->dxn_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_bwd(m, 1, L.proj[QLC_LLAMA_UP], k.xn_mlp_b, m->du_b, T, m->dxn2_b, QLC_DTYPE_BF16));
-        QLC_TRY(lanes_join(m, 1));
-        // dx_mid = rmsnorm_backward(x_mid, dxn + dxn2) + dx   (residual)
-        LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_mid), cf2(L.mlp_norm), cb2(m->dxn_b), cb2(m->dxn2_b),
-           (const __nv_bfloat162 *)nullptr, c.rms_eps, cf2(dx), f2(dx_alt), b2(dx_alt_b), T, h2);
+        if (uses_gate_up(L)) {
+            // dg | du as one (T, 2I) matrix: the merged layer's input-gradient GEMM contracts over both
+            LK(swiglu_bwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
+               reinterpret_cast<const uint4 *>(k.gate_b + I), reinterpret_cast<const uint4 *>(m->d_act_b),
+               reinterpret_cast<uint4 *>(m->dg_b), reinterpret_cast<uint4 *>(m->dg_b + I), T * I / 8, (uint32_t)(I / 8),
+               (uint32_t)(2 * I / 8));
+            QLC_TRY(pipe_bwd(m, 0, L.gate_up, k.xn_mlp_b, m->dg_b, T, m->dxn_b, QLC_DTYPE_BF16));
+            // dx_mid = rmsnorm_backward(x_mid, dxn) + dx   (residual)
+            LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_mid), cf2(L.mlp_norm), cb2(m->dxn_b), (const __nv_bfloat162 *)nullptr,
+               (const __nv_bfloat162 *)nullptr, c.rms_eps, cf2(dx), f2(dx_alt), b2(dx_alt_b), T, h2);
+        } else {
+            LK(swiglu_bwd_bf16_kernel, blocks_for(T * I / 8, 256), 256, reinterpret_cast<const uint4 *>(k.gate_b),
+               reinterpret_cast<const uint4 *>(k.up_b), reinterpret_cast<const uint4 *>(m->d_act_b),
+               reinterpret_cast<uint4 *>(m->dg_b), reinterpret_cast<uint4 *>(m->du_b), T * I / 8, (uint32_t)(I / 8),
+               (uint32_t)(I / 8));
+            QLC_TRY(lanes_fork(m, 1));
+            QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_GATE], k.xn_mlp_b, m->dg_b, T, m->dxn_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_bwd(m, 1, L.proj[QLC_LLAMA_UP], k.xn_mlp_b, m->du_b, T, m->dxn2_b, QLC_DTYPE_BF16));
+            QLC_TRY(lanes_join(m, 1));
+            // dx_mid = rmsnorm_backward(x_mid, dxn + dxn2) + dx   (residual)
+            LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_mid), cf2(L.mlp_norm), cb2(m->dxn_b), cb2(m->dxn2_b),
+               (const __nv_bfloat162 *)nullptr, c.rms_eps, cf2(dx), f2(dx_alt), b2(dx_alt_b), T, h2);
+        }
         // attention branch (llama.rs:577-601); dO arrives as bf16 straight from the output projection's dX GEMM
         QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_O], k.attn_out_b, dx_alt_b, T, m->d_attn_b, QLC_DTYPE_BF16));
         QLC_TRY(attention_tc_backward(m->ctx, k.qr_b, k.kr_b, k.v_b, nullptr, nullptr, k.attn_out_b, m->d_attn_b, k.lse, m->delta,
@@ -1494,6 +1536,7 @@ int qlc_llama_destroy(qlc_llama *m) {
         cudaFree(L.attn_norm);
         cudaFree(L.mlp_norm);
         for (qlc_layer *p : L.proj) qlc_layer_destroy(p);
+        qlc_layer_destroy(L.gate_up);
     }
     cudaFree(m->d_embed);
     cudaFree(m->d_embed_bf16);
@@ -1505,6 +1548,43 @@ int qlc_llama_destroy(qlc_llama *m) {
 
 // quantize == nullptr: every projection is NF4-quantised; otherwise projection k is quantised iff quantize[k] != 0
 // and kept as a raw fp32 matrix (llama.rs:87-93, Proj::Raw) otherwise.
+// (Re)builds L.gate_up from the gate and up layers: possible when both are quantised the same way and gate's element
+// count is a whole number of quantisation blocks and (double quantisation) of 256-block groups, so that the flat
+// blocking of the concatenated (2I, h) matrix (quant.rs:100-118, 283-299) is the two matrices' blockings one after
+// the other.  The payload is copied, not re-quantised: the merged layer multiplies by the very same weights.
+static int build_gate_up(qlc_llama *m, LlamaLayer &L) {
+    qlc_layer_destroy(L.gate_up);
+    L.gate_up = nullptr;
+    const qlc_layer *g = L.proj[QLC_LLAMA_GATE], *u = L.proj[QLC_LLAMA_UP];
+    if (!g || !u || !g->w || !u->w || g->r || u->r) return QLC_OK;
+    const qlc_qtensor *qg = g->w, *qu = u->w;
+    if (qg->block_size != qu->block_size || qg->dq != qu->dq || qg->n != qu->n || qg->cols != qu->cols) return QLC_OK;
+    if (qg->n % qg->block_size || (qg->n & 1) || (qg->dq && qg->nb % 256)) return QLC_OK;
+    qlc_qtensor *q = nullptr;
+    QLC_TRY(alloc_qtensor(m->ctx, qg->rows + qu->rows, qg->cols, qg->block_size, qg->dq, &q));
+    cudaStream_t st = m->ctx->stream;
+    int rc = QLC_OK;
+    auto copy = [&](void *dst, const void *src, size_t bytes) {
+        if (rc == QLC_OK && bytes && cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+            rc = fail(QLC_ERR_GPU, "copy of a quantised payload failed");
+    };
+    copy(q->d_codes, qg->d_codes, qg->n / 2);
+    copy(q->d_codes + qg->n / 2, qu->d_codes, qu->n / 2);
+    if (qg->dq) {
+        copy(q->d_absmax_codes, qg->d_absmax_codes, qg->nb);
+        copy(q->d_absmax_codes + qg->nb, qu->d_absmax_codes, qu->nb);
+        copy(q->d_absmax2, qg->d_absmax2, qg->nb / 256 * 4);
+        copy(q->d_absmax2 + qg->nb / 256, qu->d_absmax2, qu->nb / 256 * 4);
+    } else {
+        copy(q->d_scales_f32, qg->d_scales_f32, qg->nb * 4);
+        copy(q->d_scales_f32 + qg->nb, qu->d_scales_f32, qu->nb * 4);
+    }
+    if (rc == QLC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(QLC_ERR_GPU, "copy of a quantised payload failed");
+    if (rc == QLC_OK) rc = qlc_layer_create(m->ctx, q, nullptr, 0, nullptr, 0, 0, 0.0f, &L.gate_up);
+    qlc_qtensor_destroy(q);  // the layer holds its own reference on success
+    return rc;
+}
+
 static int set_layer_impl(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
                           const float *const *weights, const int *quantize, size_t block_size, int double_quant) {
     if (!m || !attn_norm || !mlp_norm || !weights) return fail(QLC_ERR_INVALID_CONFIG, "null argument");
@@ -1537,7 +1617,7 @@ static int set_layer_impl(qlc_llama *m, size_t li, const float *attn_norm, const
         qlc_layer_destroy(L.proj[k]);
         L.proj[k] = nl;
     }
-    return QLC_OK;
+    return build_gate_up(m, L);
 }
 
 int qlc_llama_set_layer(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
@@ -1573,6 +1653,7 @@ int qlc_llama_attach_adapter(qlc_llama *m, size_t li, int kind, const float *a, 
     }
     qlc_layer_destroy(old);
     m->layers[li].proj[kind] = nl;
+    if (kind == QLC_LLAMA_GATE || kind == QLC_LLAMA_UP) return build_gate_up(m, m->layers[li]);  // (drops the merged layer)
     return QLC_OK;
 }
 
