@@ -81,6 +81,11 @@ impl GpuContext {
         check(unsafe { ffi::qlc_ctx_set_reserved_sms(self.raw, sms) })
     }
 
+    /// Blocks until the asynchronous submission that returned `ticket` has delivered its outputs to host memory.
+    pub fn wait(&self, ticket: u64) -> Result<(), QloraError> {
+        check(unsafe { ffi::qlc_ctx_wait(self.raw, ticket) })
+    }
+
     /// Waits for everything queued on the context's stream and reports a status raised by a kernel.
     pub fn synchronize(&self) -> Result<(), QloraError> {
         check(unsafe { ffi::qlc_ctx_synchronize(self.raw) })

@@ -34,6 +34,11 @@ pub struct qlc_layer {
 pub struct qlc_adam {
     _private: [u8; 0],
 }
+#[repr(C)]
+pub struct qlc_comm {
+    _private: [u8; 0],
+}
+pub const QLC_COMM_ID_BYTES: usize = 128;
 
 #[repr(C)]
 #[derive(Clone, Copy)]
@@ -196,4 +201,23 @@ extern "C" {
         stats: *mut qlc_adam_stats,
     ) -> c_int;
     pub fn qlc_adam_state_bytes(opt: *const qlc_adam) -> usize;
+
+    // bf16 / fp32 host buffers through the row-slab pipelines; forward + backward of one batch in one call
+    // (X crosses the host link once), synchronous and asynchronous (ticket) forms
+    pub fn qlc_qlora_forward_host(ctx: *mut qlc_ctx, layer: *mut qlc_layer, x: *const c_void, dtype: c_int, batch: usize, y: *mut c_void) -> c_int;
+    pub fn qlc_qlora_backward_host(ctx: *mut qlc_ctx, layer: *mut qlc_layer, x: *const c_void, dy: *const c_void, dtype: c_int, batch: usize, grad_x: *mut c_void, grad_a: *mut c_float, grad_b: *mut c_float) -> c_int;
+    pub fn qlc_qlora_forward_backward_host(ctx: *mut qlc_ctx, layer: *mut qlc_layer, x: *const c_void, dy: *const c_void, dtype: c_int, batch: usize, y: *mut c_void, grad_x: *mut c_void, grad_a: *mut c_float, grad_b: *mut c_float) -> c_int;
+    pub fn qlc_qlora_forward_backward_host_async(ctx: *mut qlc_ctx, layer: *mut qlc_layer, x: *const c_void, dy: *const c_void, dtype: c_int, batch: usize, y: *mut c_void, grad_x: *mut c_void, grad_a: *mut c_float, grad_b: *mut c_float, ticket: *mut u64) -> c_int;
+    pub fn qlc_ctx_wait(ctx: *mut qlc_ctx, ticket: u64) -> c_int;
+
+    // optimiser state to and from host memory (checkpoint / resume)
+    pub fn qlc_adam_get_state(opt: *mut qlc_adam, index: usize, numel: *mut usize, step: *mut u64, m_codes: *mut u8, v_codes: *mut u8, m_scales: *mut c_float, v_scales: *mut c_float) -> c_int;
+    pub fn qlc_adam_set_state(opt: *mut qlc_adam, index: usize, numel: usize, step: u64, m_codes: *const u8, v_codes: *const u8, m_scales: *const c_float, v_scales: *const c_float) -> c_int;
+
+    // gradient exchange between the ranks of a data-parallel job (NCCL, loaded at first use)
+    pub fn qlc_comm_unique_id(id_out: *mut u8, id_len: usize) -> c_int;
+    pub fn qlc_comm_init(ctx: *mut qlc_ctx, nranks: c_int, rank: c_int, id: *const u8, id_len: usize, out: *mut *mut qlc_comm) -> c_int;
+    pub fn qlc_comm_allreduce_sum_f32(comm: *mut qlc_comm, d_buf: *mut c_float, count: usize) -> c_int;
+    pub fn qlc_allreduce_lora_grads(comm: *mut qlc_comm, layer: *mut qlc_layer) -> c_int;
+    pub fn qlc_comm_destroy(comm: *mut qlc_comm) -> c_int;
 }

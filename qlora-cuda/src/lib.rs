@@ -26,4 +26,4 @@ pub use kernels::{
     gpu_dequantize, gpu_matmul, gpu_matmul_trans_a, gpu_matmul_trans_b, gpu_qlora_backward,
     gpu_qlora_forward,
 };
-pub use resident::{CudaPagedAdam, CudaQloraLinear};
+pub use resident::{Bf16Grads, CudaPagedAdam, CudaQloraLinear, StepBuffers};

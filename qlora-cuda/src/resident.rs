@@ -83,10 +83,83 @@ impl<'c> CudaQloraLinear<'c> {
         Ok(QloraGrads { grad_a, grad_b, grad_x })
     }
 
+    /// Forward and backward of one batch of bf16 activations (raw bf16 bit patterns) in one call: the same results
+    /// as `gpu_qlora_forward` followed by `gpu_qlora_backward` (kernels.rs:262-353), but X crosses the host link once.
+    pub fn forward_backward_bf16(&self, x: &[u16], dy: &[u16], batch: usize) -> Result<(Vec<u16>, Bf16Grads), QloraError> {
+        if x.len() != batch * self.in_dim || dy.len() != batch * self.out_dim {
+            return Err(QloraError::ShapeMismatch(format!(
+                "x.len() = {}, dy.len() = {} but batch*in_dim = {}, batch*out_dim = {}",
+                x.len(), dy.len(), batch * self.in_dim, batch * self.out_dim
+            )));
+        }
+        let mut y = vec![0u16; batch * self.out_dim];
+        let mut grad_x = vec![0u16; batch * self.in_dim];
+        let mut grad_a = (self.rank > 0).then(|| vec![0.0f32; self.rank * self.in_dim]);
+        let mut grad_b = (self.rank > 0).then(|| vec![0.0f32; self.out_dim * self.rank]);
+        let pa = grad_a.as_mut().map_or(ptr::null_mut(), |v| v.as_mut_ptr());
+        let pb = grad_b.as_mut().map_or(ptr::null_mut(), |v| v.as_mut_ptr());
+        check(unsafe {
+            ffi::qlc_qlora_forward_backward_host(
+                self.ctx.raw(),
+                self.dev.raw,
+                x.as_ptr().cast(),
+                dy.as_ptr().cast(),
+                ffi::QLC_DTYPE_BF16,
+                batch,
+                y.as_mut_ptr().cast(),
+                grad_x.as_mut_ptr().cast(),
+                pa,
+                pb,
+            )
+        })?;
+        Ok((y, Bf16Grads { grad_a, grad_b, grad_x }))
+    }
+
+    /// The same call without waiting: the buffers of `io` must stay untouched until `GpuContext::wait(ticket)` has
+    /// returned.  A caller that keeps two submissions in flight, each on its own `StepBuffers`, keeps the host link
+    /// busy in both directions.
+    ///
+    /// # Safety
+    /// `io` is borrowed by the device until the ticket has been waited for.
+    pub unsafe fn submit_forward_backward_bf16(&self, io: &mut StepBuffers, batch: usize) -> Result<u64, QloraError> {
+        let mut ticket = 0u64;
+        check(ffi::qlc_qlora_forward_backward_host_async(
+            self.ctx.raw(),
+            self.dev.raw,
+            io.x.as_ptr().cast(),
+            io.dy.as_ptr().cast(),
+            ffi::QLC_DTYPE_BF16,
+            batch,
+            io.y.as_mut_ptr().cast(),
+            io.grad_x.as_mut_ptr().cast(),
+            io.grad_a.as_mut_ptr(),
+            io.grad_b.as_mut_ptr(),
+            &mut ticket,
+        ))?;
+        Ok(ticket)
+    }
+
     /// `LoraAdapter::set_weights` through `adapter_mut` (lora.rs:70-83, qlora.rs:175-177).
     pub fn set_adapter_weights(&mut self, a: &[f32], b: &[f32]) -> Result<(), QloraError> {
         check(unsafe { ffi::qlc_layer_set_weights(self.dev.raw, a.as_ptr(), a.len(), b.as_ptr(), b.len()) })
     }
+}
+
+/// Gradients of the bf16 calls: `grad_x` as bf16 bit patterns, adapter gradients in fp32 (`QloraGrads`, qlora.rs:13-20).
+pub struct Bf16Grads {
+    pub grad_a: Option<Vec<f32>>,
+    pub grad_b: Option<Vec<f32>>,
+    pub grad_x: Vec<u16>,
+}
+
+/// Host buffers of one asynchronous step (allocate them page-locked for full link speed).
+pub struct StepBuffers {
+    pub x: Vec<u16>,
+    pub dy: Vec<u16>,
+    pub y: Vec<u16>,
+    pub grad_x: Vec<u16>,
+    pub grad_a: Vec<f32>,
+    pub grad_b: Vec<f32>,
 }
 
 /// `Adam8bit` (qlora-core/src/optim.rs:143-204) with its 8-bit state on the device, or paged through

@@ -13,7 +13,7 @@ import os
 
 import pytest
 
-REF_TEST = "/root/reference/qlora-python/tests/test_qlora.py"
+REF_TEST = os.path.join(os.environ.get("QLORA_REFERENCE_TREE", "/root/reference"), "qlora-python", "tests", "test_qlora.py")
 
 
 @pytest.mark.skipif(not os.path.exists(REF_TEST), reason="the reference tree is not on this machine")
