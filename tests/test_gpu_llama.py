@@ -325,3 +325,51 @@ def test_merged_gate_up_layer_equals_the_two_layers(v):
         as_, bs = separate.adapter_grads(li, kind, rank)
         assert rel_fro(am, as_) <= 1e-2 and rel_fro(bm, bs) <= 1e-2, (li, kind, rel_fro(am, as_), rel_fro(bm, bs))
         assert rel_fro(am, ga) <= 5e-2 and rel_fro(bm, gb) <= 5e-2, (li, kind, rel_fro(am, ga), rel_fro(bm, gb))
+
+
+def _qkv_case(v, out_path=None):
+    """Logits and q / v adapter gradients of a small model on the bf16 pipeline (a fixed seeded case)."""
+    kw = dict(hidden=128, layers=2, heads=2, kv_heads=1, intermediate=256, vocab=128)
+    rank, alpha, n_seq, seq_len = 8, 16.0, 2, 150
+    rng = np.random.default_rng(21)
+    ids = rng.integers(0, kw["vocab"], n_seq * seq_len)
+    dlogits = (rng.standard_normal((n_seq * seq_len, kw["vocab"])) * 0.1).astype(np.float32)
+    ctx = v.GpuContext(0)
+    ctx.set_precision(v.PRECISION_BF16)
+    m, ref, cfg = _build(v, ctx, kw, seed=53, rank=rank, alpha=alpha)
+    out = {"logits": m.forward(ids, n_seq, seq_len)}
+    m.backward(ids, dlogits, n_seq, seq_len)
+    for li in range(cfg.layers):
+        for kind in ("q", "v"):
+            out[f"ga_{li}_{kind}"], out[f"gb_{li}_{kind}"] = m.adapter_grads(li, kind, rank)
+    if out_path:
+        np.savez(out_path, **out)
+    return out, (ref, ids, n_seq, seq_len, dlogits)
+
+
+@pytest.mark.gpu
+def test_merged_qkv_layer_equals_the_three_layers(v, tmp_path):
+    """q, k and v run as ONE layer in the bf16 pipeline (codes side by side, fp32 block scales decoded from the three
+    payloads, the adapters of q and v stacked into one rank-16 adapter with zero blocks).  The same case computed by
+    a second process with QLC_LLAMA_NO_QKV=1 (three layers, three GEMMs each way): logits bit-identical (the zero
+    blocks add exact zeros), adapter gradients equal up to the bf16 rounding of the three input gradients that the
+    merged layer sums in one accumulator; both within the usual bounds of the oracle."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = str(tmp_path / "separate.npz")
+    env = dict(os.environ, QLC_LLAMA_NO_QKV="1")
+    code = ("import sys; sys.path.insert(0, %r); sys.path.insert(0, %r); import vkqlora.rs_b200 as v; "
+            "import test_gpu_llama as t; t._qkv_case(v, %r)") % (os.path.dirname(here), here, path)
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=300)
+    merged, (ref, ids, n_seq, seq_len, dlogits) = _qkv_case(v)
+    with np.load(path) as sep:
+        assert np.array_equal(merged["logits"], sep["logits"])
+        for k in merged:
+            if k != "logits":
+                assert rel_fro(merged[k], sep[k]) <= 1e-2, (k, rel_fro(merged[k], sep[k]))
+    want_logits, want_grads = _oracle_batch(ref, ids, n_seq, seq_len, dlogits)
+    assert rel_fro(merged["logits"], want_logits) <= 2e-2
+    for (li, kind), (ga, gb) in want_grads.items():
+        assert rel_fro(merged[f"ga_{li}_{kind}"], ga) <= 5e-2 and rel_fro(merged[f"gb_{li}_{kind}"], gb) <= 5e-2, (li, kind)

@@ -324,7 +324,8 @@ __global__ void attn_bwd_finish_kernel(const float *__restrict__ dqr, const floa
                                        const float *__restrict__ dv_parts, size_t part_stride, int parts,
                                        const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                        __nv_bfloat16 *__restrict__ dq_b, __nv_bfloat16 *__restrict__ dk_b,
-                                       __nv_bfloat16 *__restrict__ dv_b, size_t tokens, int heads, int kv_heads, int seq_len) {
+                                       __nv_bfloat16 *__restrict__ dv_b, size_t tokens, int heads, int kv_heads, int seq_len,
+                                       size_t ld_q, size_t ld_kv) {  // row strides of dq_b and of dk_b / dv_b (elements)
     pdl_trigger();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -341,7 +342,7 @@ __global__ void attn_bwd_finish_kernel(const float *__restrict__ dqr, const floa
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] += x[e];
         }
-        *reinterpret_cast<uint4 *>(dv_b + at) = pack8(acc);
+        *reinterpret_cast<uint4 *>(dv_b + t * ld_kv + (size_t)(rem - (heads + kv_heads) * 4) * 8) = pack8(acc);
         return;
     }
     const int hh = rem >> 2, j0 = (rem & 3) * 8;
@@ -377,9 +378,136 @@ __global__ void attn_bwd_finish_kernel(const float *__restrict__ dqr, const floa
         lo[e] = a[e] * c[e] + b[e] * sn[e];
         hi[e] = b[e] * c[e] - a[e] * sn[e];
     }
-    __nv_bfloat16 *y = is_q ? dq_b : dk_b;
-    *reinterpret_cast<uint4 *>(y + at) = pack8(lo);
-    *reinterpret_cast<uint4 *>(y + at + kHeadDim / 2) = pack8(hi);
+    __nv_bfloat16 *y = is_q ? dq_b + t * ld_q + (size_t)hh * kHeadDim + j0 : dk_b + t * ld_kv + (size_t)(hh - heads) * kHeadDim + j0;
+    *reinterpret_cast<uint4 *>(y) = pack8(lo);
+    *reinterpret_cast<uint4 *>(y + kHeadDim / 2) = pack8(hi);
+}
+
+// Forward RoPE of the merged q | k | v projection's output (rows of ld elements: q heads, k heads, v heads): q and k
+// rotated into their own matrices, v copied into its own (the attention kernels read three dense matrices).
+__global__ void rope_qkv_kernel(const __nv_bfloat16 *__restrict__ qkv, size_t ld, const float *__restrict__ cos_t,
+                                const float *__restrict__ sin_t, __nv_bfloat16 *__restrict__ yq, __nv_bfloat16 *__restrict__ yk,
+                                __nv_bfloat16 *__restrict__ yv, size_t tokens, int heads, int kv_heads, int seq_len) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_token = (heads + kv_heads) * 4 + kv_heads * 8;
+    if (i >= tokens * per_token) return;
+    const size_t t = i / per_token;
+    const int rem = (int)(i % per_token);
+    const __nv_bfloat16 *row = qkv + t * ld;
+    if (rem >= (heads + kv_heads) * 4) {  // v: 8 values per thread
+        const size_t c = (size_t)(rem - (heads + kv_heads) * 4) * 8;
+        *reinterpret_cast<uint4 *>(yv + t * kv_heads * kHeadDim + c) =
+            *reinterpret_cast<const uint4 *>(row + (size_t)(heads + kv_heads) * kHeadDim + c);
+        return;
+    }
+    const int hh = rem >> 2, j0 = (rem & 3) * 8;
+    const bool is_q = hh < heads;
+    const __nv_bfloat16 *x = row + (size_t)hh * kHeadDim + j0;  // k heads follow the q heads in the row
+    __nv_bfloat16 *y = is_q ? yq + (t * heads + hh) * kHeadDim + j0 : yk + (t * kv_heads + (hh - heads)) * kHeadDim + j0;
+    const int pos = (int)(t % seq_len);
+    float a[8], b[8], c[8], sn[8], lo[8], hi[8];
+    load8(x, a);
+    load8(x + kHeadDim / 2, b);
+    load8(cos_t + pos * (kHeadDim / 2) + j0, c);
+    load8(sin_t + pos * (kHeadDim / 2) + j0, sn);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        lo[e] = a[e] * c[e] - b[e] * sn[e];
+        hi[e] = b[e] * c[e] + a[e] * sn[e];
+    }
+    *reinterpret_cast<uint4 *>(y) = pack8(lo);
+    *reinterpret_cast<uint4 *>(y + kHeadDim / 2) = pack8(hi);
+}
+
+// The merged q | k | v layer's adapter operands (zero-padded bf16 A, B and B^T) from the projections' own fp32 A / B:
+// A_m stacks the A matrices, B_m holds each B in its rows and rank columns, zeros elsewhere.
+struct QkvRefresh {
+    const float *a[3], *b[3];
+    uint32_t r[3], out[3];  // ranks and output widths of q, k, v
+    __nv_bfloat16 *a_pad, *b_pad, *bt_pad;
+    uint32_t r_pad, in_dim, out_m;
+};
+constexpr int kQkvBatch = 24;
+struct QkvRefreshBatch {
+    int n;
+    QkvRefresh d[kQkvBatch];
+};
+__global__ void qkv_refresh_kernel(const QkvRefreshBatch batch) {
+    pdl_trigger();
+    pdl_wait();
+    const QkvRefresh &d = batch.d[blockIdx.y];
+    const size_t na = (size_t)d.r_pad * d.in_dim, nb = (size_t)d.out_m * d.r_pad;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < na + 2 * nb; i += (size_t)gridDim.x * blockDim.x) {
+        float val = 0.0f;
+        if (i < na) {
+            const uint32_t r = (uint32_t)(i / d.in_dim), c = (uint32_t)(i % d.in_dim);
+            uint32_t r0 = 0;
+            for (int sgm = 0; sgm < 3; ++sgm) {
+                if (r < r0 + d.r[sgm]) {
+                    val = d.a[sgm][(size_t)(r - r0) * d.in_dim + c];
+                    break;
+                }
+                r0 += d.r[sgm];
+            }
+            d.a_pad[i] = __float2bfloat16_rn(val);
+            continue;
+        }
+        const bool transposed = i >= na + nb;
+        const size_t j = i - na - (transposed ? nb : 0);
+        const uint32_t row = transposed ? (uint32_t)(j % d.out_m) : (uint32_t)(j / d.r_pad);
+        const uint32_t c = transposed ? (uint32_t)(j / d.out_m) : (uint32_t)(j % d.r_pad);
+        uint32_t o0 = 0, r0 = 0;
+        for (int sgm = 0; sgm < 3; ++sgm) {
+            if (row < o0 + d.out[sgm]) {
+                if (c >= r0 && c < r0 + d.r[sgm]) val = d.b[sgm][(size_t)(row - o0) * d.r[sgm] + (c - r0)];
+                break;
+            }
+            o0 += d.out[sgm];
+            r0 += d.r[sgm];
+        }
+        (transposed ? d.bt_pad : d.b_pad)[j] = __float2bfloat16_rn(val);
+    }
+}
+
+// The merged layer's adapter gradients back into the projections' own gradient buckets (grad_A, then grad_B):
+// grad_A of a projection is its rows of the merged grad_A; grad_B its rows and rank columns of the merged grad_B.
+struct QkvScatter {
+    const float *ga_m, *gb_m;
+    float *bucket[3];
+    uint32_t r[3], out[3];
+    uint32_t r_m, in_dim;
+};
+struct QkvScatterBatch {
+    int n;
+    QkvScatter d[kQkvBatch];
+};
+__global__ void qkv_scatter_kernel(const QkvScatterBatch batch) {
+    pdl_trigger();
+    pdl_wait();
+    const QkvScatter &d = batch.d[blockIdx.y];
+    size_t total = 0;
+    for (int sgm = 0; sgm < 3; ++sgm) total += (size_t)d.r[sgm] * (d.in_dim + d.out[sgm]);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t k = i;
+        uint32_t o0 = 0, r0 = 0;
+        for (int sgm = 0; sgm < 3; ++sgm) {
+            const size_t na = (size_t)d.r[sgm] * d.in_dim, nb = (size_t)d.out[sgm] * d.r[sgm];
+            if (k < na + nb) {
+                if (k < na) {
+                    d.bucket[sgm][k] = d.ga_m[(size_t)r0 * d.in_dim + k];  // rows r0.. of the merged grad_A, contiguous
+                } else {
+                    const size_t j = k - na, row = j / d.r[sgm], c = j % d.r[sgm];
+                    d.bucket[sgm][k] = d.gb_m[(size_t)(o0 + row) * d.r_m + r0 + c];
+                }
+                break;
+            }
+            k -= na + nb;
+            o0 += d.out[sgm];
+            r0 += d.r[sgm];
+        }
+    }
 }
 
 // gate / up (and dg / du below) are read with a row stride of ld8 16-byte words, cols8 words per row: two (T, I)
@@ -907,6 +1035,10 @@ struct LlamaLayer {
     // the other), built when that concatenation equals quantising the two matrices separately; the bf16 pipeline
     // then runs one forward GEMM and one input-gradient GEMM (contraction over both) instead of two each
     qlc_layer *gate_up = nullptr;
+    // q, k and v as ONE layer (h + 2 kv output features; fp32 block scales, decoded from the three payloads, so no
+    // alignment of the double-quantisation groups is needed) whose adapter stacks the projections' adapters: one
+    // forward GEMM, one input-gradient GEMM, one pair of LoRA side launches instead of three / two each
+    qlc_layer *qkv = nullptr;
     LlamaCache c;
 };
 struct qlc_llama {
@@ -934,6 +1066,7 @@ struct qlc_llama {
     bool want_bf16_logits = false, logits_are_bf16 = false;
     __nv_bfloat16 *dx_b = nullptr, *dx2_b = nullptr, *d_act_b = nullptr, *dg_b = nullptr, *du_b = nullptr, *dq_b = nullptr,
                   *dk_b = nullptr, *dv_b = nullptr, *q_tmp_b = nullptr, *k_tmp_b = nullptr, *tmp_b = nullptr, *dxn_b = nullptr,
+                  *qkv_b = nullptr, *dqkv_b = nullptr,  // (T, h + 2 kv): output / upstream gradient of the merged q | k | v layer
                   *dxn2_b = nullptr, *dxn3_b = nullptr;
     float *cos_t = nullptr, *sin_t = nullptr;
     // backward scratch
@@ -1054,6 +1187,8 @@ int ensure_capacity(qlc_llama *m, size_t n_seq, size_t seq_len) {
         for (float **p : hs) QLC_TRY(dev_alloc_t(m, p, T * h));
         QLC_TRY(dev_alloc_t(m, &m->dkr, T * kv));
         QLC_TRY(dev_alloc_t(m, &m->k_tmp_b, T * kv));
+        QLC_TRY(dev_alloc_t(m, &m->qkv_b, T * (h + 2 * kv)));
+        QLC_TRY(dev_alloc_t(m, &m->dqkv_b, T * (h + 2 * kv)));
         __nv_bfloat16 **hb[] = {&m->dx_b, &m->dx2_b, &m->dq_b, &m->q_tmp_b, &m->tmp_b, &m->dxn_b, &m->dxn2_b, &m->dxn3_b};
         for (__nv_bfloat16 **p : hb) QLC_TRY(dev_alloc_t(m, p, T * h));
         QLC_TRY(dev_alloc_t(m, &m->dk_b, T * kv));
@@ -1192,6 +1327,76 @@ bool uses_gate_up(const LlamaLayer &L) {
            L.proj[QLC_LLAMA_UP]->r == 0;
 }
 
+bool uses_qkv(const LlamaLayer &L) {
+    static const bool off = getenv("QLC_LLAMA_NO_QKV") != nullptr;  // diagnostics
+    return !off && L.qkv != nullptr;
+}
+
+// Rebuilds the adapter operands of every merged q | k | v layer from the projections' current fp32 A / B
+// (they change with every optimiser step, and a caller may change them through the projections' handles).
+int refresh_qkv_operands(qlc_llama *m) {
+    cudaStream_t st = m->ctx->stream;
+    static thread_local QkvRefreshBatch batch;
+    batch.n = 0;
+    auto flush = [&]() -> int {
+        if (!batch.n) return QLC_OK;
+        LK(qkv_refresh_kernel, dim3(8, (unsigned)batch.n), 256, batch);
+        batch.n = 0;
+        return QLC_OK;
+    };
+    for (LlamaLayer &L : m->layers) {
+        if (!uses_qkv(L) || !L.qkv->r) continue;
+        QkvRefresh &d = batch.d[batch.n++];
+        const int kinds[3] = {QLC_LLAMA_Q, QLC_LLAMA_K, QLC_LLAMA_V};
+        for (int i = 0; i < 3; ++i) {
+            const qlc_layer *P = L.proj[kinds[i]];
+            d.a[i] = P->d_a;
+            d.b[i] = P->d_b;
+            d.r[i] = (uint32_t)P->r;
+            d.out[i] = (uint32_t)P->out_dim;
+        }
+        d.a_pad = L.qkv->d_a_pad;
+        d.b_pad = L.qkv->d_b_pad;
+        d.bt_pad = L.qkv->d_bt_pad;
+        d.r_pad = (uint32_t)L.qkv->r_pad;
+        d.in_dim = (uint32_t)L.qkv->in_dim;
+        d.out_m = (uint32_t)L.qkv->out_dim;
+        if (batch.n == kQkvBatch) QLC_TRY(flush());
+    }
+    return flush();
+}
+
+// After the backward pass: the merged layers' adapter gradients go to the projections' own buckets, where the
+// optimiser, the gradient exchange and the getters expect them.
+int scatter_qkv_grads(qlc_llama *m) {
+    cudaStream_t st = m->ctx->stream;
+    static thread_local QkvScatterBatch batch;
+    batch.n = 0;
+    auto flush = [&]() -> int {
+        if (!batch.n) return QLC_OK;
+        LK(qkv_scatter_kernel, dim3(8, (unsigned)batch.n), 256, batch);
+        batch.n = 0;
+        return QLC_OK;
+    };
+    for (LlamaLayer &L : m->layers) {
+        if (!uses_qkv(L) || !L.qkv->r) continue;
+        QkvScatter &d = batch.d[batch.n++];
+        d.ga_m = L.qkv->d_grad_bucket;
+        d.gb_m = L.qkv->d_grad_bucket + L.qkv->r * L.qkv->in_dim;
+        const int kinds[3] = {QLC_LLAMA_Q, QLC_LLAMA_K, QLC_LLAMA_V};
+        for (int i = 0; i < 3; ++i) {
+            qlc_layer *P = L.proj[kinds[i]];
+            d.bucket[i] = P->d_grad_bucket;
+            d.r[i] = (uint32_t)P->r;
+            d.out[i] = (uint32_t)P->out_dim;
+        }
+        d.r_m = (uint32_t)L.qkv->r;
+        d.in_dim = (uint32_t)L.qkv->in_dim;
+        if (batch.n == kQkvBatch) QLC_TRY(flush());
+    }
+    return flush();
+}
+
 int pipe_fwd(qlc_llama *m, int lane, qlc_layer *L, const __nv_bfloat16 *x, size_t T, void *y, int y_dtype) {
     return umma_qlora_forward(lane_ctx(m, lane), L, x, T, y, y_dtype, false);
 }
@@ -1215,6 +1420,7 @@ int run_forward_pipeline(qlc_llama *m, size_t n_seq, size_t seq_len) {
     __nv_bfloat162 *const no_bf16x2 = nullptr;
     const bool head_bf16 = head_uses_bf16(m);
     QLC_TRY(ensure_lanes(m));
+    QLC_TRY(refresh_qkv_operands(m));
     auto f2 = [](float *p) { return reinterpret_cast<float2 *>(p); };
     auto cf2 = [](const float *p) { return reinterpret_cast<const float2 *>(p); };
     auto b2 = [](__nv_bfloat16 *p) { return reinterpret_cast<__nv_bfloat162 *>(p); };
@@ -1231,13 +1437,21 @@ int run_forward_pipeline(qlc_llama *m, size_t n_seq, size_t seq_len) {
         LlamaLayer &L = m->layers[li];
         LlamaCache &k = L.c;
         const bool last = li + 1 == m->layers.size();
-        QLC_TRY(lanes_fork(m, 2));
-        QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_Q], k.xn_attn_b, T, m->q_tmp_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_fwd(m, 1, L.proj[QLC_LLAMA_K], k.xn_attn_b, T, m->k_tmp_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_fwd(m, 2, L.proj[QLC_LLAMA_V], k.xn_attn_b, T, k.v_b, QLC_DTYPE_BF16));
-        QLC_TRY(lanes_join(m, 2));
-        LK(rope_qk_kernel<__nv_bfloat16>, blocks_for(T * (c.heads + c.kv_heads) * 4, 256), 256, (const __nv_bfloat16 *)m->q_tmp_b,
-           (const __nv_bfloat16 *)m->k_tmp_b, m->cos_t, m->sin_t, k.qr_b, k.kr_b, T, (int)c.heads, (int)c.kv_heads, (int)seq_len, 0);
+        if (uses_qkv(L)) {
+            QLC_TRY(pipe_fwd(m, 0, L.qkv, k.xn_attn_b, T, m->qkv_b, QLC_DTYPE_BF16));  // (T, h + 2 kv): q | k | v
+            LK(rope_qkv_kernel, blocks_for(T * ((c.heads + c.kv_heads) * 4 + c.kv_heads * 8), 256), 256,
+               (const __nv_bfloat16 *)m->qkv_b, h + 2 * m->kv_dim, m->cos_t, m->sin_t, k.qr_b, k.kr_b, k.v_b, T, (int)c.heads,
+               (int)c.kv_heads, (int)seq_len);
+        } else {
+            QLC_TRY(lanes_fork(m, 2));
+            QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_Q], k.xn_attn_b, T, m->q_tmp_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_fwd(m, 1, L.proj[QLC_LLAMA_K], k.xn_attn_b, T, m->k_tmp_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_fwd(m, 2, L.proj[QLC_LLAMA_V], k.xn_attn_b, T, k.v_b, QLC_DTYPE_BF16));
+            QLC_TRY(lanes_join(m, 2));
+            LK(rope_qk_kernel<__nv_bfloat16>, blocks_for(T * (c.heads + c.kv_heads) * 4, 256), 256,
+               (const __nv_bfloat16 *)m->q_tmp_b, (const __nv_bfloat16 *)m->k_tmp_b, m->cos_t, m->sin_t, k.qr_b, k.kr_b, T,
+               (int)c.heads, (int)c.kv_heads, (int)seq_len, 0);
+        }
         QLC_TRY(attention_tc_forward(m->ctx, k.qr_b, k.kr_b, k.v_b, nullptr, k.attn_out_b, k.lse, n_seq, seq_len, c.heads,
                                      c.kv_heads));
         QLC_TRY(pipe_fwd(m, 0, L.proj[QLC_LLAMA_O], k.attn_out_b, T, m->tmp_b, QLC_DTYPE_BF16));
@@ -1322,20 +1536,33 @@ int run_backward_pipeline(qlc_llama *m, size_t n_seq, size_t seq_len, bool dlogi
         QLC_TRY(attention_tc_backward(m->ctx, k.qr_b, k.kr_b, k.v_b, nullptr, nullptr, k.attn_out_b, m->d_attn_b, k.lse, m->delta,
                                       m->dqr, nullptr, nullptr, nullptr, m->dk_parts, m->dv_parts, n_seq, seq_len, c.heads,
                                       c.kv_heads, m->lane[0], m->ev_main, m->ev_lane[0]));
-        LK(attn_bwd_finish_kernel, blocks_for(T * ((c.heads + c.kv_heads) * 4 + c.kv_heads * 8), 256), 256,
-           (const float *)m->dqr, (const float *)m->dk_parts, (const float *)m->dv_parts, T * m->kv_dim,
-           (int)(c.heads / c.kv_heads), m->cos_t, m->sin_t, m->dq_b, m->dk_b, m->dv_b, T, (int)c.heads, (int)c.kv_heads,
-           (int)seq_len);
-        QLC_TRY(lanes_fork(m, 2));
-        QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_Q], k.xn_attn_b, m->dq_b, T, m->dxn_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_bwd(m, 1, L.proj[QLC_LLAMA_K], k.xn_attn_b, m->dk_b, T, m->dxn2_b, QLC_DTYPE_BF16));
-        QLC_TRY(pipe_bwd(m, 2, L.proj[QLC_LLAMA_V], k.xn_attn_b, m->dv_b, T, m->dxn3_b, QLC_DTYPE_BF16));
-        QLC_TRY(lanes_join(m, 2));
-        // dx_in = rmsnorm_backward(x_in, dxn + dxn2 + dxn3) + dx_mid
-        LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_in), cf2(L.attn_norm), cb2(m->dxn_b), cb2(m->dxn2_b), cb2(m->dxn3_b),
-           c.rms_eps, cf2(dx_alt), f2(dx), b2(dx_b), T, h2);
+        if (uses_qkv(L)) {
+            // dq | dk | dv as one (T, h + 2 kv) matrix: the merged layer's input-gradient GEMM contracts over all three
+            const size_t ldm = h + 2 * m->kv_dim;
+            LK(attn_bwd_finish_kernel, blocks_for(T * ((c.heads + c.kv_heads) * 4 + c.kv_heads * 8), 256), 256,
+               (const float *)m->dqr, (const float *)m->dk_parts, (const float *)m->dv_parts, T * m->kv_dim,
+               (int)(c.heads / c.kv_heads), m->cos_t, m->sin_t, m->dqkv_b, m->dqkv_b + h, m->dqkv_b + h + m->kv_dim, T,
+               (int)c.heads, (int)c.kv_heads, (int)seq_len, ldm, ldm);
+            QLC_TRY(pipe_bwd(m, 0, L.qkv, k.xn_attn_b, m->dqkv_b, T, m->dxn_b, QLC_DTYPE_BF16));
+            // dx_in = rmsnorm_backward(x_in, dxn) + dx_mid
+            LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_in), cf2(L.attn_norm), cb2(m->dxn_b), (const __nv_bfloat162 *)nullptr,
+               (const __nv_bfloat162 *)nullptr, c.rms_eps, cf2(dx_alt), f2(dx), b2(dx_b), T, h2);
+        } else {
+            LK(attn_bwd_finish_kernel, blocks_for(T * ((c.heads + c.kv_heads) * 4 + c.kv_heads * 8), 256), 256,
+               (const float *)m->dqr, (const float *)m->dk_parts, (const float *)m->dv_parts, T * m->kv_dim,
+               (int)(c.heads / c.kv_heads), m->cos_t, m->sin_t, m->dq_b, m->dk_b, m->dv_b, T, (int)c.heads, (int)c.kv_heads,
+               (int)seq_len, h, m->kv_dim);
+            QLC_TRY(lanes_fork(m, 2));
+            QLC_TRY(pipe_bwd(m, 0, L.proj[QLC_LLAMA_Q], k.xn_attn_b, m->dq_b, T, m->dxn_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_bwd(m, 1, L.proj[QLC_LLAMA_K], k.xn_attn_b, m->dk_b, T, m->dxn2_b, QLC_DTYPE_BF16));
+            QLC_TRY(pipe_bwd(m, 2, L.proj[QLC_LLAMA_V], k.xn_attn_b, m->dv_b, T, m->dxn3_b, QLC_DTYPE_BF16));
+            QLC_TRY(lanes_join(m, 2));
+            // dx_in = rmsnorm_backward(x_in, dxn + dxn2 + dxn3) + dx_mid
+            LK(pipe_norm_bwd_kernel, rows_grid, 256, cf2(k.x_in), cf2(L.attn_norm), cb2(m->dxn_b), cb2(m->dxn2_b), cb2(m->dxn3_b),
+               c.rms_eps, cf2(dx_alt), f2(dx), b2(dx_b), T, h2);
+        }
     }
-    return QLC_OK;
+    return scatter_qkv_grads(m);
 }
 
 int run_forward(qlc_llama *m, size_t n_seq, size_t seq_len) {
@@ -1537,6 +1764,7 @@ int qlc_llama_destroy(qlc_llama *m) {
         cudaFree(L.mlp_norm);
         for (qlc_layer *p : L.proj) qlc_layer_destroy(p);
         qlc_layer_destroy(L.gate_up);
+        qlc_layer_destroy(L.qkv);
     }
     cudaFree(m->d_embed);
     cudaFree(m->d_embed_bf16);
@@ -1582,6 +1810,69 @@ static int build_gate_up(qlc_llama *m, LlamaLayer &L) {
     if (rc == QLC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(QLC_ERR_GPU, "copy of a quantised payload failed");
     if (rc == QLC_OK) rc = qlc_layer_create(m->ctx, q, nullptr, 0, nullptr, 0, 0, 0.0f, &L.gate_up);
     qlc_qtensor_destroy(q);  // the layer holds its own reference on success
+    if (rc == QLC_OK && !umma_fused_supported(L.gate_up)) {
+        qlc_layer_destroy(L.gate_up);
+        L.gate_up = nullptr;
+    }
+    return rc;
+}
+
+// (Re)builds L.qkv from the q, k and v layers.  The merged (h + 2 kv, h) weight carries fp32 block scales, decoded
+// from each projection's payload exactly as dequantisation decodes them (quant.rs:212-221), so it multiplies by the
+// very same weights whatever the projections' double-quantisation grouping; each projection must hold a whole
+// number of quantisation blocks.  The merged adapter (rank = the sum of the ranks, at most 64) needs one common
+// alpha / r; its operands are rebuilt from the projections' A / B before every forward pass.
+static int build_qkv(qlc_llama *m, LlamaLayer &L) {
+    qlc_layer_destroy(L.qkv);
+    L.qkv = nullptr;
+    const int kinds[3] = {QLC_LLAMA_Q, QLC_LLAMA_K, QLC_LLAMA_V};
+    size_t rows = 0, r_m = 0, n_total = 0, nb_total = 0;
+    float scale = 0.0f;
+    for (int i = 0; i < 3; ++i) {
+        const qlc_layer *P = L.proj[kinds[i]];
+        if (!P || !P->w) return QLC_OK;
+        const qlc_qtensor *q = P->w;
+        if (q->block_size != L.proj[QLC_LLAMA_Q]->w->block_size || q->n % q->block_size || (q->n & 1)) return QLC_OK;
+        rows += q->rows;
+        n_total += q->n;
+        nb_total += q->nb;
+        if (P->r) {
+            const float sc = P->alpha / (float)P->r;  // lora.rs:64-66
+            if (r_m && sc != scale) return QLC_OK;
+            scale = sc;
+            r_m += P->r;
+        }
+    }
+    if (r_m > 64) return QLC_OK;
+    const size_t h = m->cfg.hidden;
+    qlc_qtensor *q = nullptr;
+    QLC_TRY(alloc_qtensor(m->ctx, rows, h, L.proj[QLC_LLAMA_Q]->w->block_size, false, &q));
+    cudaStream_t st = m->ctx->stream;
+    int rc = QLC_OK;
+    size_t e0 = 0, b0 = 0;
+    for (int i = 0; i < 3 && rc == QLC_OK; ++i) {
+        const qlc_qtensor *src = L.proj[kinds[i]]->w;
+        if (cudaMemcpyAsync(q->d_codes + e0 / 2, src->d_codes, src->n / 2, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+            rc = fail(QLC_ERR_GPU, "copy of a quantised payload failed");
+        if (rc == QLC_OK) rc = launch_decode_block_scales(m->ctx, src, q->d_scales_f32 + b0);
+        e0 += src->n;
+        b0 += src->nb;
+    }
+    if (rc == QLC_OK && r_m) {
+        std::vector<float> a0(r_m * h, 0.0f), b0v(rows * r_m, 0.0f);  // placeholders: the operands come from the projections
+        rc = qlc_layer_create(m->ctx, q, a0.data(), a0.size(), b0v.data(), b0v.size(), r_m, scale * (float)r_m, &L.qkv);
+    } else if (rc == QLC_OK) {
+        rc = qlc_layer_create(m->ctx, q, nullptr, 0, nullptr, 0, 0, 0.0f, &L.qkv);
+    }
+    if (rc == QLC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(QLC_ERR_GPU, "building the merged q | k | v layer failed");
+    qlc_qtensor_destroy(q);  // the layer holds its own reference on success
+    // the common scale must survive the round trip through alpha, and the fused kernels must take the merged shape
+    if (rc == QLC_OK && ((L.qkv->r && L.qkv->alpha / (float)L.qkv->r != scale) || !umma_fused_supported(L.qkv))) {
+        qlc_layer_destroy(L.qkv);
+        L.qkv = nullptr;
+    }
+    (void)n_total;
+    (void)nb_total;
     return rc;
 }
 
@@ -1617,7 +1908,8 @@ static int set_layer_impl(qlc_llama *m, size_t li, const float *attn_norm, const
         qlc_layer_destroy(L.proj[k]);
         L.proj[k] = nl;
     }
-    return build_gate_up(m, L);
+    QLC_TRY(build_gate_up(m, L));
+    return build_qkv(m, L);
 }
 
 int qlc_llama_set_layer(qlc_llama *m, size_t li, const float *attn_norm, const float *mlp_norm,
@@ -1654,6 +1946,7 @@ int qlc_llama_attach_adapter(qlc_llama *m, size_t li, int kind, const float *a, 
     qlc_layer_destroy(old);
     m->layers[li].proj[kind] = nl;
     if (kind == QLC_LLAMA_GATE || kind == QLC_LLAMA_UP) return build_gate_up(m, m->layers[li]);  // (drops the merged layer)
+    if (kind == QLC_LLAMA_Q || kind == QLC_LLAMA_K || kind == QLC_LLAMA_V) return build_qkv(m, m->layers[li]);
     return QLC_OK;
 }
 
