@@ -1340,7 +1340,7 @@ int refresh_qkv_operands(qlc_llama *m) {
     batch.n = 0;
     auto flush = [&]() -> int {
         if (!batch.n) return QLC_OK;
-        LK(qkv_refresh_kernel, dim3(8, (unsigned)batch.n), 256, batch);
+        LK(qkv_refresh_kernel, dim3(40, (unsigned)batch.n), 256, batch);
         batch.n = 0;
         return QLC_OK;
     };
