@@ -1592,6 +1592,33 @@ int umma_gemm_bf16(qlc_ctx *ctx, const __nv_bfloat16 *d_a, const __nv_bfloat16 *
     a.out = d_c;
     a.ldo = (uint32_t)N;
     a.out_bf16 = c_bf16 ? 1 : 0;  // the result as fp32 or rounded to bf16
+    // The persistent paired-CTA kernel takes a plain bf16 B operand as well: its LoRA extension steps fetch both
+    // operands by TMA, so a GEMM whose whole contraction is "extension" (no weight steps, the producer warps only
+    // pass the stage barriers on) runs with the paired MMAs, the one-wave item walk and the overlapped epilogue.
+    static const bool plain_one_cta = getenv("QLC_PLAIN_GEMM_ONE_CTA") != nullptr;  // diagnostics
+    if (use_paired_ctas() && !plain_one_cta && N % 64 == 0) {
+        GemmArgs p{};
+        p.splits = 1;
+        p.a_rows = 128;
+        p.out_scale = 1.0f;
+        p.status = ctx->d_status;
+        p.M = (uint32_t)M;
+        p.N = (uint32_t)N;
+        p.w_rows = b_is_kn ? (uint32_t)K : (uint32_t)N;
+        p.w_cols = b_is_kn ? (uint32_t)N : (uint32_t)K;
+        p.blk_shift = 6;
+        p.k_steps = 0;
+        p.ext_steps = (uint32_t)(K / 64);
+        p.out = d_c;
+        p.ldo = (uint32_t)N;
+        p.out_bf16 = c_bf16 ? 1 : 0;
+        if (!b_is_kn) {
+            QLC_TRY(make_map(&tB, d_b, N, K, 128));
+            return launch_gemm2<false>(ctx, 0, tA, tA, tB, p, nullptr);
+        }
+        QLC_TRY(make_map(&tB, d_b, K, N, 64));
+        return launch_gemm2<true>(ctx, 0, tA, tA, tB, p, nullptr);
+    }
     if (!b_is_kn) {
         QLC_TRY(make_map(&tB, d_b, N, K, 256));
         return launch_gemm<256, 2, false, false, false, 3>(ctx, 0, tA, tB, tA, tB, a);
