@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the QloraLinear hot path (BASELINE config 2): one step = forward + backward of a
+"""Benchmark of the QloraLinear hot path (benchmark configuration 2): one step = forward + backward of a
 4096x4096 NF4 (block 64, double-quantised) QloraLinear with a rank-16 LoRA adapter over 8192 token
 rows, bf16 activations, synthetic seeded data.
 
@@ -586,7 +586,7 @@ C5_WORKLOAD = ("Llama-7B projection stack (q,k,v,o 4096x4096; gate,up 11008x4096
 
 
 def measure_stack(v, dist_, steps, warmup):
-    """BASELINE config 5: the seven Llama-7B projections (q/k/v/o 4096x4096, gate/up 11008x4096, down
+    """benchmark configuration 5: the seven Llama-7B projections (q/k/v/o 4096x4096, gate/up 11008x4096, down
     4096x11008), NF4 + double quant, LoRA r=64 on all; 65536 token rows per step split evenly over the
     ranks (strong scaling); each projection is an independent QloraLinear fwd+bwd with its own bf16 X and
     dY.  The LoRA gradients of all projections live in one fp32 bucket (4 997 120 floats) that is summed over
@@ -721,7 +721,7 @@ def model_cpu_baseline(cfg, r, alpha, seq_len=256):
 
 
 def measure_model(v, dist_, steps, warmup, model_layers, with_e2e=True, with_cpu=True):
-    """BASELINE config 4: SmolLM-135M-shaped QLoRA training step, random init (no checkpoint is involved):
+    """benchmark configuration 4: SmolLM-135M-shaped QLoRA training step, random init (no checkpoint is involved):
     30 Llama layers, hidden 576, 9 heads / 3 KV heads, MLP 1536 SwiGLU, vocab 49152, RMSNorm, RoPE; all linears
     NF4 block 64 + double quant, Q/V LoRA r=8 alpha=16; token ids uniform over the vocabulary, 16 sequences of
     512 tokens per GPU; one step = forward + cross-entropy + backward + 8-bit Adam (max_resident_pages=4: the
@@ -835,7 +835,7 @@ def model_arm(args, dist_):
 
 # ---------------------------------------------------------------------------------------------
 def measure_quant_sweep(v, dist_, sizes, iters):
-    """Standalone quantize_nf4 / dequantize sweep (BASELINE config 2b): GB/s of algorithmic bytes
+    """Standalone quantize_nf4 / dequantize sweep (benchmark configuration 2b): GB/s of algorithmic bytes
     (quantize 4.51587 B/elem; dequantize 0.51587 + 4 (fp32) or + 2 (bf16) B/elem)."""
     import torch
 
@@ -910,7 +910,7 @@ def quant_sweep_arm(args, dist_):
 
 
 def measure_adam(v, dist_, variants, steps):
-    """Paged 8-bit Adam (BASELINE config 3): 112 tensors x 262144 fp32 (28 layers x Q/V x {A 64x4096, B 4096x64}),
+    """Paged 8-bit Adam (benchmark configuration 3): 112 tensors x 262144 fp32 (28 layers x Q/V x {A 64x4096, B 4096x64}),
     block 256, lr 1e-3, betas 0.9/0.999, eps 1e-8; once fully resident and once with max_resident_pages=4
     (every state page is evicted to pinned host memory each step).  Algorithmic traffic 16 B/elem + 16 B/block."""
     import torch

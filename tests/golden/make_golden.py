@@ -32,7 +32,7 @@ QUANT_CASES = {  # name -> (weights factory, rows, cols, block_size, double_quan
 }
 
 LAYER_CASES = {  # name -> (out_dim, in_dim, r, batch, alpha)
-    "c1_576": (576, 576, 8, 32, 16.0),  # BASELINE config 1
+    "c1_576": (576, 576, 8, 32, 16.0),  # benchmark configuration 1
     "odd_18x20": (18, 20, 5, 3, 8.0),   # qlora-wgpu/tests/gpu_backward.rs:60
     "tiny_3x4": (3, 4, 2, 2, 8.0),      # qlora-core/tests/qlora.rs:91
 }

@@ -133,7 +133,7 @@ def test_ref_converges_and_state_is_compact(v):  # tests/optim.rs:89-131
 
 
 def test_forced_eviction_many_tensors_bitwise(v, oracle):
-    """A scaled-down BASELINE config 3: many tensors, max_resident_pages=4 so every state page is
+    """A scaled-down benchmark configuration 3: many tensors, max_resident_pages=4 so every state page is
     evicted to pinned host memory each step; results must equal the resident run and the oracle."""
     sizes = [65536 + 256 * (i % 3) for i in range(12)]
     paged = v.Adam8bit(v.AdamConfig(max_resident_pages=4))
@@ -215,7 +215,7 @@ def test_state_save_restore_continues_bitwise(v, oracle):
 
 
 def test_full_size_config3_bitwise(v, oracle):
-    """BASELINE config 3 at full size: 112 tensors x 262 144 fp32 (28 layers x Q/V x {A 64x4096, B 4096x64}),
+    """benchmark configuration 3 at full size: 112 tensors x 262 144 fp32 (28 layers x Q/V x {A 64x4096, B 4096x64}),
     block 256, 3 steps, fully resident and with max_resident_pages=4 (every page evicted to pinned host memory
     each step), on device buffers as the benchmark runs it.  Parameters and 8-bit state of both runs equal the
     CPU oracle's bit for bit; the oracle steps a sample of the tensors (all tensors are independent)."""

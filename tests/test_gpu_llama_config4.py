@@ -1,4 +1,4 @@
-"""Model-level parity at the dimensions of BASELINE config 4 (SmolLM-135M shape: hidden 576, 9 query heads on 3
+"""Model-level parity at the dimensions of benchmark configuration 4 (SmolLM-135M shape: hidden 576, 9 query heads on 3
 key/value heads, MLP 1536, vocabulary 49 152) and in the reference's own projection modes.
 
   * one and two decoder layers at the full width, 2 sequences of 192 tokens (three 64-position attention tiles,

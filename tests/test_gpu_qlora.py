@@ -148,7 +148,7 @@ def _assert_close(name, got, want, rows, cols, tol=TOL_BF16):
     (256, 256, 0, 256),     # main GEMM only, one tile
     (256, 256, 16, 256),    # + LoRA extension
     (512, 320, 8, 300),     # ragged rows, several k-steps, two column tiles
-    (576, 576, 8, 32),      # BASELINE config 1 shape: partial column tile, few rows
+    (576, 576, 8, 32),      # benchmark configuration 1 shape: partial column tile, few rows
     (320, 1024, 64, 1000),  # rank 64
     (256, 256, 5, 70),      # the reference GPU test's rank (qlora-wgpu/tests/gpu_backward.rs:60)
     (320, 256, 96, 300),    # ranks above 64: the rank-padded products run in 64-column slices
@@ -244,7 +244,7 @@ def test_tensor_core_path_other_block_sizes(v, oracle, tc_ctx, block_size, doubl
 
 
 def test_tensor_core_full_size_4096_sampled_rows(v, oracle, tc_ctx):
-    """BASELINE config 2 (4096x4096, 8192 rows, r=16, alpha=32) through the host bf16 entry point.
+    """benchmark configuration 2 (4096x4096, 8192 rows, r=16, alpha=32) through the host bf16 entry point.
     Rows of Y and dX are independent, so a seeded sample of rows (plus tile-edge rows) is compared
     with the oracle; grad_A / grad_B contract over all rows and are compared in full."""
     out_dim = in_dim = 4096
@@ -400,7 +400,7 @@ def test_async_fused_host_calls_two_in_flight(v, oracle, tc_ctx):
 
 @pytest.mark.parametrize("out_dim,in_dim", [(11008, 4096), (4096, 11008)])
 def test_tensor_core_projection_stack_shapes_rank64(v, oracle, tc_ctx, out_dim, in_dim):
-    """BASELINE config 5 shapes (gate/up 11008x4096, down 4096x11008; r=64, alpha=128): 43 column tiles
+    """benchmark configuration 5 shapes (gate/up 11008x4096, down 4096x11008; r=64, alpha=128): 43 column tiles
     (not a multiple of anything convenient), a ragged last row tile, cut tiles in the last wave.
     Sampled rows of Y / dX against the oracle; grad_A / grad_B in full against float64 numpy."""
     batch, r, alpha = 1000, 64, 128.0
@@ -440,7 +440,7 @@ def tf32_ctx(v):
     (256, 256, 0, 256),     # weight GEMM only
     (256, 256, 16, 256),    # + LoRA (rank 16: narrow side products)
     (512, 320, 8, 300),     # ragged rows, several k-steps, two column tiles
-    (576, 576, 8, 32),      # BASELINE config 1 shape
+    (576, 576, 8, 32),      # benchmark configuration 1 shape
     (320, 1024, 64, 1000),  # rank 64, cut tiles
     (320, 256, 96, 300),    # rank above 64 (two 64-column slices)
 ])
