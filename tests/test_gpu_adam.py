@@ -293,3 +293,35 @@ def test_adam_bitwise_outside_the_fast_windows(v, oracle):
             oopt.step(p2, [g])
             assert np.array_equal(p1[0].view(np.uint32), p2[0].view(np.uint32)), (cfg, t)
         _compare_state(opt, oopt, 0)
+
+
+@pytest.mark.parametrize("mode", ["slots", "hybrid"])
+def test_paged_modes_match_resident_bitwise(mode, tmp_path):
+    """QLC_ADAM_PAGED_MODE is read once per process, so the two copy-based forms of a paged step (pages through
+    device slots both ways / on the way in only) run in a process of their own: parameters and 8-bit state after
+    three steps equal the resident optimiser's bit for bit, as in the default (in-place) form the other tests use."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    code = f"""
+import sys; sys.path.insert(0, {os.path.dirname(here)!r}); sys.path.insert(0, {here!r})
+import numpy as np, vkqlora.rs_b200 as v
+from refdata import normal
+sizes = [300000, 77, 4096 + 13, 1100000]
+a = v.Adam8bit(v.AdamConfig(max_resident_pages=2)); b = v.Adam8bit(v.AdamConfig())
+pa = [normal(30 + i, n, 0.01) for i, n in enumerate(sizes)]; pb = [p.copy() for p in pa]
+for t in range(3):
+    g = [normal(500 * t + i, n, 0.01) for i, n in enumerate(sizes)]
+    a.step(pa, g); b.step(pb, g)
+for i in range(len(sizes)):
+    assert np.array_equal(pa[i].view(np.uint32), pb[i].view(np.uint32)), i
+    sa, sb = a.get_state(i), b.get_state(i)
+    for k in ("m_codes", "v_codes", "m_scales", "v_scales"):
+        assert np.array_equal(sa[k], sb[k]), (i, k)
+assert a.paging_info()["host_bytes"] > 0
+print("ok")
+"""
+    env = dict(os.environ, QLC_ADAM_PAGED_MODE=mode)
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]

@@ -373,3 +373,33 @@ def test_merged_qkv_layer_equals_the_three_layers(v, tmp_path):
     assert rel_fro(merged["logits"], want_logits) <= 2e-2
     for (li, kind), (ga, gb) in want_grads.items():
         assert rel_fro(merged[f"ga_{li}_{kind}"], ga) <= 5e-2 and rel_fro(merged[f"gb_{li}_{kind}"], gb) <= 5e-2, (li, kind)
+
+
+@pytest.mark.gpu
+def test_adapters_with_different_scales_keep_three_layers(v):
+    """q and v adapters with different alpha / r cannot share one merged adapter: the block keeps q, k and v as three
+    layers (and still merges gate / up), and matches the oracle as before."""
+    from vkqlora.rs_b200 import llama
+    kw = dict(hidden=128, layers=2, heads=2, kv_heads=1, intermediate=256, vocab=128)
+    rank, n_seq, seq_len = 8, 2, 150
+    ocfg = nl.LlamaConfig(**kw)
+    ref = nl.random_model(ocfg, seed=59, targets=("q", "v"), rank=rank, alpha=16.0, scale=0.08)
+    ctx = v.GpuContext(0)
+    ctx.set_precision(v.PRECISION_BF16)
+    m = llama.LlamaModel(llama.LlamaConfig(**kw), ref.embed, ref.final_norm, ctx)
+    for li, L in enumerate(ref.layers):
+        m.set_layer(li, L.attn_norm, L.mlp_norm, {k: L.proj[k].w for k in nl.KINDS})
+        L.proj["v"].alpha = 24.0     # alpha / r = 3 for v, 2 for q
+        for k in ("q", "v"):
+            m.attach_adapter(li, k, L.proj[k].a, L.proj[k].b, rank, L.proj[k].alpha)
+        for k in nl.KINDS:
+            L.proj[k].w = m.dequantized_weight(li, k)
+    rng = np.random.default_rng(17)
+    ids = rng.integers(0, kw["vocab"], n_seq * seq_len)
+    dlogits = (rng.standard_normal((n_seq * seq_len, kw["vocab"])) * 0.1).astype(np.float32)
+    want_logits, want_grads = _oracle_batch(ref, ids, n_seq, seq_len, dlogits)
+    assert rel_fro(m.forward(ids, n_seq, seq_len), want_logits) <= 2e-2
+    m.backward(ids, dlogits, n_seq, seq_len)
+    for (li, kind), (ga, gb) in want_grads.items():
+        a, b = m.adapter_grads(li, kind, rank)
+        assert rel_fro(a, ga) <= 5e-2 and rel_fro(b, gb) <= 5e-2, (li, kind, rel_fro(a, ga), rel_fro(b, gb))

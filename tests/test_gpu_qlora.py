@@ -470,3 +470,27 @@ def _tf32_case(v, oracle, tf32_ctx, out_dim, in_dim, r, batch, cfg):
     if r:
         _assert_close("grad_a", g.grad_a, ga, r, in_dim, tol=TOL_TF32)
         _assert_close("grad_b", g.grad_b, gb, out_dim, r, tol=TOL_TF32)
+
+
+def test_reserved_sms_leave_results_unchanged(v, oracle, tc_ctx):
+    """qlc_ctx_set_reserved_sms only changes how many CTA pairs walk the tile list of the weight GEMMs: the results of
+    a shape with several tiles per pair are bit-identical with 0, 4 and 40 SMs reserved; bad values are refused."""
+    out_dim, in_dim, r, batch = 1024, 512, 16, 9000   # 18 row tiles x 4 column tiles = 72 tiles, k-cut candidates
+    layer, wd, x, dy, a, b, alpha = _tc_case(v, oracle, tc_ctx, out_dim, in_dim, r, batch, seed=61)
+    results = []
+    for sms in (0, 4, 40):
+        tc_ctx.set_reserved_sms(sms)
+        y = layer.forward(x, batch)
+        g = layer.backward(x, dy, batch)
+        results.append((y, g.grad_x))
+    tc_ctx.set_reserved_sms(0)
+    for y, gx in results[1:]:
+        # (tiles cut along the contraction are summed in chunk order whatever the pair count: still bit-identical
+        #  unless the cut plan itself changes with the pair count, hence the tolerance on top of exact equality)
+        assert np.array_equal(y, results[0][0]) or rel_fro(y, results[0][0]) <= 1e-6
+        assert np.array_equal(gx, results[0][1]) or rel_fro(gx, results[0][1]) <= 1e-6
+    _assert_close("forward", results[1][0], oracle.qlora_forward(x, batch, wd, out_dim, in_dim, a, b, r, alpha, threads=8), batch, out_dim)
+    with pytest.raises(v.InvalidConfig):
+        tc_ctx.set_reserved_sms(-2)
+    with pytest.raises(v.InvalidConfig):
+        tc_ctx.set_reserved_sms(10**6)
